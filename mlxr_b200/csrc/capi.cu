@@ -45,6 +45,7 @@ struct Workspace {
   uint32_t* sync = nullptr;  // kSyncWords zero-initialised words (counters, barriers)
   int* status = nullptr;     // device status word
   int* status_host = nullptr;  // pinned mirror
+  uint32_t bar_host = 0;     // host mirror of sync[0], the decode kernel's grid-barrier counter
 };
 static std::mutex g_ws_mu;
 static std::map<std::pair<int, void*>, Workspace> g_ws;
@@ -117,8 +118,18 @@ static int check_quant(int qt, int K, int group_size, bool check_group) {
 }
 
 // Kernel selection for one linear.  Fast kernels need 16-byte aligned rows.
+// The first kDecodeScratchBytes of a workspace's scratch belong to the decode kernel's
+// split-K partial sums; intermediates of the fused entry points start after them.
 static int run_linear(const void* x, const void* w, const void* bias, void* y, int M, int N, int K,
                       int qt, int dtype, cudaStream_t st) {
+  if (M > 0 && N > 0 && decode_supported(qt, M, K, &w, 1)) {
+    Workspace* ws = nullptr;
+    if (int r = get_workspace(st, kDecodeScratchBytes, &ws)) return r;
+    DecodeLinear L;
+    memset(&L, 0, sizeof(L));
+    L.w[0] = w; L.rows[0] = N; L.nmat = 1; L.K = K; L.x = x; L.y[0] = y; L.bias[0] = bias;
+    return launch_decode(&L, 1, M, qt, dtype, ws->buf, kDecodeScratchBytes, ws->sync, &ws->bar_host, ws->status, st);
+  }
   return launch_qgemm_generic(x, w, bias, y, M, N, K, qt, dtype, st);
 }
 
@@ -307,8 +318,19 @@ int mlxr_mlp_block(const void* x, const void* norm_weight, const void* w_gate, c
   const size_t n_bytes = align_up((size_t)M * hidden * es, 256);
   const size_t i_bytes = align_up((size_t)M * inter * es, 256);
   Workspace* ws = nullptr;
-  if (int r = get_workspace(st, n_bytes + 2 * i_bytes, &ws)) return r;
-  char* base = (char*)ws->buf;
+  if (int r = get_workspace(st, kDecodeScratchBytes + n_bytes + 2 * i_bytes, &ws)) return r;
+  char* base = (char*)ws->buf + kDecodeScratchBytes;
+  const void* wgu[2] = {w_gate, w_up};
+  if (decode_supported(qt, M, hidden, wgu, 2) && decode_supported(qt, M, inter, &w_down, 1)) {
+    // one persistent launch: [RMSNorm ->] gate/up -> SiLU*up -> grid barrier -> down
+    DecodeLinear L[2];
+    memset(L, 0, sizeof(L));
+    L[0].w[0] = w_gate; L[0].w[1] = w_up; L[0].rows[0] = L[0].rows[1] = inter; L[0].nmat = 2;
+    L[0].interleave = 1; L[0].K = hidden; L[0].x = x; L[0].gamma = norm_weight; L[0].eps = eps;
+    L[0].y[0] = base;  // h [M, inter], lives in L2 between the phases
+    L[1].w[0] = w_down; L[1].rows[0] = hidden; L[1].nmat = 1; L[1].K = inter; L[1].x = base; L[1].y[0] = y;
+    return launch_decode(L, 2, M, qt, dtype, ws->buf, kDecodeScratchBytes, ws->sync, &ws->bar_host, ws->status, st);
+  }
   void* nbuf = base;
   void* gbuf = base + n_bytes;
   void* ubuf = base + n_bytes + i_bytes;
@@ -339,11 +361,26 @@ int mlxr_qkv_rope(const void* x, const void* norm_weight, const void* wq, const 
   cudaStream_t st = (cudaStream_t)stream;
   const size_t es = dtype_size(dtype);
   Workspace* ws = nullptr;
-  if (int r = get_workspace(st, align_up((size_t)M * hidden * es, 256), &ws)) return r;
+  if (int r = get_workspace(st, kDecodeScratchBytes + align_up((size_t)M * hidden * es, 256), &ws)) return r;
+  const void* wqkv[3] = {wq, wk, wv};
+  if (decode_supported(qt, M, hidden, wqkv, 3)) {
+    // one launch: [RMSNorm ->] q, k, v stacked along N, RoPE in the epilogue of q and k rows
+    DecodeLinear L;
+    memset(&L, 0, sizeof(L));
+    L.w[0] = wq; L.w[1] = wk; L.w[2] = wv;
+    L.rows[0] = q_heads * head_dim; L.rows[1] = L.rows[2] = kv_heads * head_dim; L.nmat = 3;
+    L.K = hidden; L.x = x; L.gamma = norm_weight; L.eps = eps;
+    L.y[0] = q_out; L.y[1] = k_out; L.y[2] = v_out;
+    L.epi[0] = L.epi[1] = 2;
+    L.cos_t = cos_f16; L.sin_t = sin_f16; L.positions = positions;
+    L.head_dim = head_dim; L.max_seq = max_seq_len; L.pos_offset = position_offset;
+    return launch_decode(&L, 1, M, qt, dtype, ws->buf, kDecodeScratchBytes, ws->sync, &ws->bar_host, ws->status, st);
+  }
+  void* nbuf = (char*)ws->buf + kDecodeScratchBytes;
   const void* n = x;
   if (norm_weight) {
-    if (int r = launch_rmsnorm(x, norm_weight, nullptr, ws->buf, M, hidden, eps, dtype, st)) return r;
-    n = ws->buf;
+    if (int r = launch_rmsnorm(x, norm_weight, nullptr, nbuf, M, hidden, eps, dtype, st)) return r;
+    n = nbuf;
   }
   if (int r = run_linear(n, wq, nullptr, q_out, M, q_heads * head_dim, hidden, qt, dtype, st)) return r;
   if (int r = run_linear(n, wk, nullptr, k_out, M, kv_heads * head_dim, hidden, qt, dtype, st)) return r;

@@ -21,4 +21,28 @@ int launch_rope(const void* x, const uint16_t* cos_t, const uint16_t* sin_t,
                 int max_seq, int mode, float scale, int offset, int dtype, int* status,
                 cudaStream_t st);
 
+// ---- persistent decode kernel (decode.cu) ---------------------------------------------------
+// One linear (or up to three stacked along N, or gate/up interleaved) of a decode phase.
+struct DecodeLinear {
+  const void* w[3];
+  int rows[3];
+  int nmat;
+  int interleave;          // gate/up in 8+8 row tiles with the SiLU(gate)*up epilogue
+  int K;
+  const void* x;           // [M, K]
+  const void* gamma;       // RMSNorm weight or null
+  float eps;
+  void* y[3];
+  const void* bias[3];
+  int epi[3];              // 0 plain, 2 RoPE
+  const uint16_t* cos_t;
+  const uint16_t* sin_t;
+  const int32_t* positions;
+  int head_dim, max_seq, pos_offset;
+};
+constexpr size_t kDecodeScratchBytes = (size_t)8 << 20;  // split-K partial sums
+bool decode_supported(int qt, int M, int K, const void* const* w, int nmat);
+int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype, void* scratch,
+                  size_t scratch_bytes, uint32_t* sync, uint32_t* bar_host, int* status, cudaStream_t st);
+
 }  // namespace mlxr
