@@ -176,6 +176,28 @@ MLXR_API int mlxr_mlp_block(const void* x, const void* norm_weight, const void* 
                             int hidden, int inter, int quant_type, float eps, int dtype,
                             void* stream);
 
+/* The same block with DENSE weights of the activation dtype and optional biases: the exact
+ * signature of swiglu_mlp() (swiglu_mlp_primitive.h:169-176), i.e.
+ * SwiGLUMLPPrimitive::eval_cpu (swiglu_mlp_primitive.mm:47-82).  w_gate, w_up:
+ * [inter, hidden]; w_down: [hidden, inter].  Not the quantized hot path: a plain
+ * fp32-accumulating kernel kept for interface completeness. */
+MLXR_API int mlxr_mlp_block_dense(const void* x, const void* w_gate, const void* w_up,
+                                  const void* w_down, const void* bias_gate, const void* bias_up,
+                                  const void* bias_down, void* y, int M, int hidden, int inter,
+                                  int dtype, void* stream);
+
+/* Synchronise `stream`, then report and clear the device status word of its workspace:
+ * MLXR_OK, MLXR_ERR_TIMEOUT (a bounded wait inside a persistent kernel gave up; results of
+ * that call are invalid) or MLXR_ERR_SHAPE (a RoPE position outside its table in a fused
+ * call).  The return value is the status of this call itself. */
+MLXR_API int mlxr_stream_status(void* stream, int* status_out);
+
+/* Timeline tracing of the persistent decode kernel (off by default).  dev_ptr: device buffer
+ * of 16 uint64 per CTA (148 * 16 * 8 bytes is enough), or NULL to switch tracing off.  Each
+ * CTA stores %globaltimer (ns) at: [0] start, [1] x prologue done, [2] first weight stage
+ * landed, [3] first tile accumulated (phase 0; +4 for phase 1), [15]/[14] end. */
+MLXR_API int mlxr_debug_set_trace_buffer(void* dev_ptr);
+
 /* Attention input projections with RoPE on q and k: n = rmsnorm(x) (norm_weight may be
  * NULL), q = n Wq^T, k = n Wk^T, v = n Wv^T, then rope_apply on q and k
  * (Attention::forward, core/graph/layers.cpp:266-278, with the rope_apply primitive).

@@ -345,6 +345,43 @@ int mlxr_mlp_block(const void* x, const void* norm_weight, const void* w_gate, c
   return run_linear(gbuf, w_down, nullptr, y, M, hidden, inter, qt, dtype, st);
 }
 
+int mlxr_mlp_block_dense(const void* x, const void* w_gate, const void* w_up, const void* w_down,
+                         const void* bias_gate, const void* bias_up, const void* bias_down, void* y, int M,
+                         int hidden, int inter, int dtype, void* stream) {
+  if (int r = check_dtype(dtype)) return r;
+  if (M < 0 || hidden <= 0 || inter <= 0) { set_error("Input must be 2D [M, hidden_size]"); return MLXR_ERR_INVALID_ARGUMENT; }
+  if (M == 0) return MLXR_OK;
+  if (!x || !w_gate || !w_up || !w_down || !y) { set_error("null pointer"); return MLXR_ERR_INVALID_ARGUMENT; }
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t i_bytes = align_up((size_t)M * inter * dtype_size(dtype), 256);
+  Workspace* ws = nullptr;
+  if (int r = get_workspace(st, kDecodeScratchBytes + 2 * i_bytes, &ws)) return r;
+  char* gbuf = (char*)ws->buf + kDecodeScratchBytes;
+  char* ubuf = gbuf + i_bytes;
+  if (int r = launch_linear_dense(x, w_gate, bias_gate, gbuf, M, inter, hidden, dtype, st)) return r;
+  if (int r = launch_linear_dense(x, w_up, bias_up, ubuf, M, inter, hidden, dtype, st)) return r;
+  if (int r = launch_swiglu(gbuf, ubuf, gbuf, (size_t)M * inter, dtype, st)) return r;
+  return launch_linear_dense(gbuf, w_down, bias_down, y, M, hidden, inter, dtype, st);
+}
+
+int mlxr_debug_set_trace_buffer(void* dev_ptr) {
+  set_decode_trace(dev_ptr);
+  return MLXR_OK;
+}
+
+int mlxr_stream_status(void* stream, int* status_out) {
+  cudaStream_t st = (cudaStream_t)stream;
+  Workspace* ws = nullptr;
+  if (int r = get_workspace(st, 0, &ws)) return r;
+  MLXR_CUDA_TRY(cudaMemcpyAsync(ws->status_host, ws->status, sizeof(int), cudaMemcpyDeviceToHost, st));
+  MLXR_CUDA_TRY(cudaMemsetAsync(ws->status, 0, sizeof(int), st));
+  MLXR_CUDA_TRY(cudaStreamSynchronize(st));
+  if (status_out) *status_out = ws->status_host[0];
+  if (ws->status_host[0] == MLXR_ERR_TIMEOUT) set_error("a bounded device-side wait expired in an earlier kernel on this stream");
+  else if (ws->status_host[0] == MLXR_ERR_SHAPE) set_error("a RoPE position (+offset) was outside [0, max_seq_len)");
+  return MLXR_OK;
+}
+
 int mlxr_qkv_rope(const void* x, const void* norm_weight, const void* wq, const void* wk, const void* wv,
                   const uint16_t* cos_f16, const uint16_t* sin_f16, const int32_t* positions, void* q_out,
                   void* k_out, void* v_out, int M, int hidden, int q_heads, int kv_heads, int head_dim,

@@ -1,7 +1,11 @@
 // Host side of the persistent decode kernel (decode_kernel.cuh): work planning
 // (K-slices, grid, shared-memory budget) and launch.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
+#include <map>
+#include <mutex>
+#include <tuple>
 
 #include "decode_kernel.cuh"
 #include "kernels.h"
@@ -10,8 +14,46 @@ namespace mlxr {
 
 using namespace decode;
 
+static unsigned long long* g_trace = nullptr;  // set by mlxr_debug_set_trace_buffer
+void set_decode_trace(void* p) { g_trace = (unsigned long long*)p; }
 static int g_num_sms = 0;
 static int g_max_smem = 0;
+
+// ---- tensor maps -----------------------------------------------------------------------------
+// A packed matrix [rows][row_bytes] is described to the TMA unit as a 2-D tensor of 8-byte
+// elements with a box of 36 x 8 (288 bytes x 8 rows).  cuTensorMapEncodeTiled is a pure host
+// function fetched from the driver at run time (no link against libcuda); maps are cached per
+// (pointer, rows, row_bytes) because weights are long-lived.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static int weight_tensor_map(const void* w, int rows, int row_bytes, CUtensorMap* out) {
+  static EncodeTiledFn encode = nullptr;
+  static std::mutex mu;
+  static std::map<std::tuple<const void*, int, int>, CUtensorMap> cache;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    MLXR_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    if (!fn || q != cudaDriverEntryPointSuccess) { set_error("cuTensorMapEncodeTiled is not available in this driver"); return MLXR_ERR_CUDA; }
+    encode = (EncodeTiledFn)fn;
+  }
+  const auto key = std::make_tuple(w, rows, row_bytes);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return MLXR_OK; }
+  const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 8), (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)(kRowStride / 8), 8};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(w), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%d) for a %d x %d byte matrix", (int)r, rows, row_bytes); return MLXR_ERR_CUDA; }
+  if (cache.size() > 4096) cache.clear();
+  cache[key] = *out;
+  return MLXR_OK;
+}
 
 static int device_props() {
   if (g_num_sms) return MLXR_OK;
@@ -24,40 +66,41 @@ static int device_props() {
 
 bool decode_supported(int qt, int M, int K, const void* const* w, int nmat) {
   if (qt != MLXR_Q4_K && qt != MLXR_Q4_0) return false;
-  if (M < 1 || M > 16 || K <= 0 || K % 256 != 0) return false;
+  if (M < 1 || M > 8 || K < 512 || K % 256 != 0) return false;   // a TMA box is two 256-blocks wide
   for (int i = 0; i < nmat; i++)
     if (((uintptr_t)w[i]) & 15u) return false;
   return true;
 }
 
-// Choose the number of K-slices S for a phase running on G CTAs (G % S == 0).  Cost =
-// rounds of items per CTA x segments per item; slices that leave consumer warps idle
-// (fewer than 6 segments per chunk) and the split-K fix-up are penalised.
-static int choose_slices(int ntiles, int nseg, int G, int mcols, int max_x_bytes, bool fixed_grid) {
+// Choose the number of K-slices S for a phase running on G CTAs with ng groups each
+// (G % S == 0).  Cost = segments streamed by the busiest CTA; the split-K fix-up and slices
+// with fewer segments than warps in a group are penalised.
+static int choose_slices(int ntiles, int nseg, int G, int ng, int M, int xrows, int max_x_bytes, bool fixed_grid) {
   double best = 1e30;
   int bestS = 0;
   for (int S = 1; S <= std::min(nseg, 16); S++) {
-    if (fixed_grid ? (G % S != 0) : false) continue;
+    if (fixed_grid && (G % S != 0)) continue;
     const int g = fixed_grid ? G : (G / S) * S;
     if (g < 1) continue;
     const int segs = (nseg + S - 1) / S;
-    if (mcols * (segs * 512 + 64) > max_x_bytes) continue;
+    if (xrows * M * (segs * 256 + 32) > max_x_bytes) continue;
     if (S > 1 && ntiles > 2000) continue;  // tile counters live in a fixed pool
-    const int rounds = (ntiles * S + g - 1) / g;
-    const int nchunks = (segs + kMaxChunkSegs - 1) / kMaxChunkSegs;
-    const int csegs = segs / nchunks;
-    double cost = (double)rounds * segs;
-    if (csegs < 6) cost *= 1.0 + 0.04 * (6 - csegs);
-    if (S > 1) cost *= 1.05;
+    const int lanes = (g / S) * ng;        // (CTA, group) pairs sharing the tiles of one slice
+    int tiles_cta0 = 0;                    // CTA 0 owns lanes 0 .. ng-1: the busiest
+    for (int gi = 0; gi < ng; gi++)
+      if (gi < ntiles) tiles_cta0 += (ntiles - 1 - gi) / lanes + 1;
+    double cost = (double)tiles_cta0 * segs;
+    if (S > 1) cost *= 1.3;                // every tile pays a fix-up round trip through L2
+    if (segs < kGroupWarps) cost *= 1.25;  // warps without a segment idle
     if (cost < best) { best = cost; bestS = S; }
   }
   return bestS;
 }
 
-
-template <int QT, typename T, int NT>
+template <int QT, typename T, int NT, int NG, bool PAIRS>
 static int launch_inst(const Params& P, const SmemPlan& plan, int G, bool cooperative, cudaStream_t st) {
-  auto kern = decode_kernel<QT, T, NT>;
+  auto kern = decode_kernel<QT, T, NT, NG, PAIRS>;
+  constexpr int kThreads = NG * kGroupWarps * 32;
   static bool attr_done[64] = {};
   int dev = 0;
   MLXR_CUDA_TRY(cudaGetDevice(&dev));
@@ -88,12 +131,24 @@ int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype
   P.gridbar = sync;
   P.bar_base = *bar_host;
   P.status = status;
-  const int NT = M <= 8 ? 1 : 2;
-  const int MC = 8 * NT;
+  P.trace = g_trace;
+  // batch <= 2 with Q4_K: pairs in the MMA columns, one n-tile per batch row
+  bool pairs = (qt == MLXR_Q4_K && M <= 2);
+  if (const char* e = getenv("MLXR_DEC_PAIRS")) pairs = pairs && atoi(e) != 0;  // tuning override
+  const int NT = pairs ? M : (M <= 4 ? 1 : 2);
+  const int xrows = pairs ? 8 : 2;
+  int NG = 2;
+  if (const char* e = getenv("MLXR_DEC_GROUPS")) { const int v = atoi(e); if (v == 1 || v == 2) NG = v; }  // tuning override
+  const int MB = 4 * NT;
+  const int auxw = qt == MLXR_Q4_K ? 4 : 8;
   int G = g_num_sms;
-  const int ring_min = 4 * kStageBytes;
-  const int fixed = MC * kConsumerWarps * kTileRows * 4 + kTileRows * MC * 4 + 1024;
-  const int max_x = g_max_smem - ring_min - fixed - MC * 64 * 4;
+  // shared memory left for the x slice when the rings keep at least two stages per warp
+  // two groups need room for 16 rings of at least two stages; otherwise run one group
+  auto x_budget = [&](int ng) {
+    const int fixed = ng * kSlots * (kGroupWarps + 1) * kTileRows * MB * 4 + 1024 + 256;
+    return g_max_smem - 2 * ng * kGroupWarps * kStageBytes - fixed - M * 64 * (auxw + 1) * 4;
+  };
+  const int max_x = x_budget(NG);
   int max_slice_segs = 0;
   size_t scratch_off = 0;
   int counter_off = 16;
@@ -110,14 +165,28 @@ int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype
       if (j < L.nmat) total_rows += L.rows[j];
     }
     ph.nmat = L.nmat;
+    for (int j = 0; j < L.nmat; j++) {
+      if (L.nmat > 1 && !L.interleave && L.rows[j] % 8 != 0) { set_error("decode kernel: stacked matrices need row counts that are multiples of 8"); return MLXR_ERR_UNSUPPORTED; }
+      if (int r = weight_tensor_map(L.w[j], L.rows[j], (L.K / 256) * kSegBytes, &P.tmap[i][j])) return r;
+    }
     ph.interleave = L.interleave;
     ph.n_total = L.interleave ? L.rows[0] : total_rows;
     ph.K = L.K;
     const int nseg = L.K / 256;
     ph.row_bytes = nseg * kSegBytes;
     ph.ntiles = L.interleave ? (ph.n_total + 7) / 8 : (ph.n_total + kTileRows - 1) / kTileRows;
-    const int S = choose_slices(ph.ntiles, nseg, G, M, max_x, nphases > 1 || i > 0);
-    if (S <= 0) { set_error("decode kernel: x slice does not fit shared memory (K=%d, M=%d)", L.K, M); return MLXR_ERR_UNSUPPORTED; }
+    int S = choose_slices(ph.ntiles, nseg, G, NG, M, xrows, max_x, nphases > 1 || i > 0);
+    if (const char* e = getenv("MLXR_DEC_S")) { const int v = atoi(e); if (v >= 1 && v <= nseg && (nphases == 1 || G % v == 0)) S = v; }  // tuning override
+    if (S <= 0) {
+      if (NG == 2 && !getenv("MLXR_DEC_GROUPS")) {   // not enough shared memory beside 16 rings: one group
+        setenv("MLXR_DEC_GROUPS", "1", 1);
+        const int rc1 = launch_decode(lin, nphases, M, qt, dtype, scratch, scratch_bytes, sync, bar_host, status, st);
+        unsetenv("MLXR_DEC_GROUPS");
+        return rc1;
+      }
+      set_error("decode kernel: x slice does not fit shared memory (K=%d, M=%d)", L.K, M);
+      return MLXR_ERR_UNSUPPORTED;
+    }
     if (nphases == 1) G = (G / S) * S;
     ph.S = S;
     ph.segs_base = nseg / S;
@@ -134,7 +203,7 @@ int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype
     ph.max_seq = L.max_seq;
     ph.pos_offset = L.pos_offset;
     if (S > 1) {
-      const size_t bytes = (size_t)S * ph.ntiles * kTileRows * MC * sizeof(float);
+      const size_t bytes = (size_t)S * ph.ntiles * kTileRows * MB * sizeof(float);
       if (scratch_off + bytes > scratch_bytes) { set_error("decode kernel: split-K scratch too small"); return MLXR_ERR_WORKSPACE; }
       ph.partials = (float*)((char*)scratch + scratch_off);
       scratch_off += (bytes + 255) & ~(size_t)255;
@@ -143,18 +212,27 @@ int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype
       counter_off += ph.ntiles;
     }
   }
-  // shared-memory plan: as many ring stages as fit
-  int stages = 12;
-  SmemPlan plan = make_plan(stages, max_slice_segs * 256, max_slice_segs, MC, M);
+  // shared-memory plan: as many ring stages per warp as fit
+  int stages = kMaxStages;
+  if (const char* e = getenv("MLXR_DEC_STAGES")) { const int v = atoi(e); if (v >= 2 && v <= kMaxStages) stages = v; }  // tuning override
+  SmemPlan plan = make_plan(NG, stages, max_slice_segs, M, MB, auxw, pairs ? 1 : 0);
   while (plan.total > g_max_smem && stages > 2) {
     stages--;
-    plan = make_plan(stages, max_slice_segs * 256, max_slice_segs, MC, M);
+    plan = make_plan(NG, stages, max_slice_segs, M, MB, auxw, pairs ? 1 : 0);
   }
   if (plan.total > g_max_smem) { set_error("decode kernel: shared memory plan does not fit"); return MLXR_ERR_UNSUPPORTED; }
   const bool coop = nphases > 1;
   int rc = MLXR_OK;
-#define INST(QT, T, NTV) rc = launch_inst<QT, T, NTV>(P, plan, G, coop, st)
-#define BY_NT(QT, T) do { if (NT == 1) INST(QT, T, 1); else INST(QT, T, 2); } while (0)
+#define INST(QT, T, NTV, NGV)                                                                      \
+  do {                                                                                             \
+    if (pairs) { if constexpr (QT == MLXR_Q4_K) rc = launch_inst<QT, T, NTV, NGV, true>(P, plan, G, coop, st); } \
+    else rc = launch_inst<QT, T, NTV, NGV, false>(P, plan, G, coop, st);                            \
+  } while (0)
+#define BY_NT(QT, T)                                                                   \
+  do {                                                                                 \
+    if (NT == 1) { if (NG == 2) INST(QT, T, 1, 2); else INST(QT, T, 1, 1); }           \
+    else { if (NG == 2) INST(QT, T, 2, 2); else INST(QT, T, 2, 1); }                   \
+  } while (0)
 #define BY_T(QT)                                                         \
   do {                                                                   \
     if (dtype == MLXR_F16) BY_NT(QT, __half);                            \

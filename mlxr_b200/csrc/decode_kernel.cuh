@@ -1,37 +1,56 @@
-// Persistent decode kernel for quantized linears at small batch (M <= 16).
+// Persistent decode kernel for quantized linears at small batch (M <= 8), Q4_K and Q4_0.
 //
-// Roofline: HBM.  One CTA per SM streams packed weight rows through a ring of shared-
-// memory stages filled by bulk async copies (cp.async.bulk, one per row segment, completion
-// on an mbarrier); eight consumer warps dequantize nibbles in registers with the
-// (x & mask) | magic half-precision trick and feed warp-level tensor-core MMAs
-// (m16n8k16, fp16 x fp16 -> fp32) in which the 16 MMA rows are 16 weight rows and the 8 MMA
-// columns are the batch.  Sub-block scales are applied to the fp32 accumulators, the
-// Q4_K min term goes through one extra k8 MMA per super-block.  Fused around it:
-//   prologue   RMSNorm of x (optional), rounding to the activation dtype, power-of-two
-//              normalisation into fp16, k-permutation into shared memory
+// Roofline: HBM.  One CTA per SM, NG groups of eight warps.  Every compute warp owns a private ring of shared-memory stages that it fills
+// itself with 2-D tensor TMA copies (cp.async.bulk.tensor.2d, one box of 8 rows x 288 bytes
+// per half tile, completion on an mbarrier) and drains itself, so nothing inside the stream
+// waits on another warp and the copy costs one instruction per stage.  A 16-row weight tile's K range is split over the eight warps of a group;
+// each leaves its partial sums in a shared-memory slot and signals a hardware named barrier;
+// the warp on duty for that tile (tile number modulo 8, so the duty rotates) waits on the
+// barrier, adds the eight partials in warp order (deterministic) and runs the epilogue and
+// the split-K fix-up.
+// (Measured and dropped: one-dimensional cp.async.bulk copies of a few hundred bytes -- an SM
+// keeps only a handful in flight, 0.5 TB/s in total; 16-byte cp.async -- the LSU needs ~14
+// cycles per 18-lane instruction, which caps the stream at 4.4 TB/s and delays every other
+// load of the SM behind the prefetch burst.)
+//
+// Arithmetic: the 4-bit codes go to the tensor cores as they are.  A 32-bit word of eight
+// nibbles is split with two masks into two u8x4 registers, which are the A fragments of
+// mma.sync.m16n8k32 (u8 x s8 -> s32; the 16 MMA rows are 16 weight rows).  The activations
+// are held as 16-bit fixed point per 256-element block (x ~ delta * xi, |xi| <= 32000),
+// split into a high and a low signed byte that sit in two adjacent MMA columns, so one MMA
+// yields sum(q * x_hi) and sum(q * x_lo) exactly and 256*hi + lo is the exact integer dot
+// product.  Sub-block scales multiply the converted sums in fp32; the "-8" offset and the
+// Q4_K min term are linear in sum(x) per sub-block and go through one fp16 k8 MMA per
+// 256-block against a table built in the prologue.
+//
+// Fused around it:
+//   prologue   RMSNorm of x (optional), rounding to the activation dtype, fixed-point split
 //   epilogue   plain (+bias) | SiLU(gate)*up on interleaved gate/up rows | RoPE on q/k rows
-//   split-K    partial sums of K-slices meet in a global scratch; the CTA that arrives last
-//              for a tile reduces them in slice order (deterministic) and runs the epilogue
-//   two phases gate/up -> grid barrier -> down in ONE launch: the producer warp keeps
-//              streaming the next phase's weights while consumers wait at the barrier
-// Every wait (mbarrier, grid barrier) is bounded; on expiry a status word is set and the
-// kernel carries on without blocking.
+//   split-K    K-slices of different CTAs meet in a global scratch; the CTA that arrives
+//              last reduces them in slice order and runs the epilogue
+//   two phases gate/up -> grid barrier -> down in ONE launch: every warp keeps its ring
+//              full with the next phase's weights while the CTA waits at the barrier
+// The only spin wait (grid barrier) is bounded; on expiry a status word is set and the
+// kernel carries on without blocking.  Named barriers involve only warps of the CTA.
 #pragma once
+#include <cuda.h>   // CUtensorMap (type only; the encoder is fetched at run time)
+
 #include "common.cuh"
 
 namespace mlxr {
 namespace decode {
 
-constexpr int kConsumerWarps = 8;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;   // + 1 producer warp
+constexpr int kGroupWarps = 8;                          // compute warps per group
 constexpr int kTileRows = 16;
-constexpr int kMaxChunkSegs = 8;                      // segments (256 k) per stage and row
-constexpr int kSegBytes = 144;                        // Q4_K super-block = 8 Q4_0 blocks
-constexpr int kRowStride = kMaxChunkSegs * kSegBytes + 16;  // 1168 B: 292 words = 4 mod 32
-constexpr int kStageBytes = kTileRows * kRowStride;   // 18688
-constexpr uint32_t kSpinLimit = 1u << 20;
+constexpr int kStageSegs = 2;                           // 256-element segments per stage and row
+constexpr int kSegBytes = 144;                          // Q4_K super-block = 8 Q4_0 blocks
+constexpr int kRowStride = kStageSegs * kSegBytes;      // 288 B: TMA boxes are dense
+constexpr int kStageBytes = kTileRows * kRowStride;     // 4608 = 36 x 128
+constexpr int kSlots = 3;                               // tiles in flight per group
+constexpr int kMaxStages = 6;
+constexpr uint32_t kSpinLimit = 1u << 22;
 
-enum Epilogue { kEpiPlain = 0, kEpiSwiglu = 1, kEpiRope = 2 };
+enum Epilogue { kEpiPlain = 0, kEpiRope = 2 };
 
 struct Phase {
   // weights: up to three packed matrices stacked along N, or gate/up interleaved in tiles
@@ -43,7 +62,7 @@ struct Phase {
   int K;
   int row_bytes;
   int ntiles;
-  int S;                 // K-slices
+  int S;                 // K-slices handled by different CTAs (gridDim.x % S == 0)
   int segs_base, segs_extra;  // slice s has segs_base + (s < segs_extra) segments
   int max_slice_segs;
   // activations
@@ -51,7 +70,7 @@ struct Phase {
   const void* gamma;     // RMSNorm weight [K] or null
   float eps;
   // outputs
-  void* y[3];            // per matrix [M, rows[i]]; swiglu: y[0] = h [M, n_total]
+  void* y[3];            // per matrix [M, rows[i]]; interleave: y[0] = h [M, n_total]
   const void* bias[3];
   int epi[3];
   // rope
@@ -60,26 +79,62 @@ struct Phase {
   const int32_t* positions;
   int head_dim, max_seq, pos_offset;
   // split-K scratch
-  float* partials;       // [S][M_pad][n_pad]
+  float* partials;       // [S][ntiles][16][MB]
   uint32_t* counters;    // [ntiles], zero between launches
 };
 
 struct Params {
+  // per phase and matrix: [rows][row_bytes / 8] of 8-byte elements, box 36 x 8 (288 B x 8 rows)
+  alignas(64) CUtensorMap tmap[2][3];
   Phase ph[2];
   int nphases;
   int M;
   uint32_t* gridbar;     // monotonically increasing arrival counter
   uint32_t bar_base;     // value of *gridbar before this launch
   int* status;
+  unsigned long long* trace;  // optional: 16 globaltimer stamps per CTA (null = off)
 };
+
+// Shared-memory plan (bytes), identical on host and device.
+struct SmemPlan {
+  int stages;        // per compute warp
+  int x_stride;      // bytes per (batch, part) row of the int8 x slice
+  int aux_stride;    // words per batch column of the sum table
+  int seg_stride;    // floats per batch column of the delta table
+  int off_ring, off_x, off_aux, off_delta, off_slots, off_tile, off_misc, total;
+};
+// aux words per segment: Q4_K 4 (pair sums hi|lo), Q4_0 8 (4 hi words + 4 lo words)
+// pairs: the batch <= 2 mapping (8 masked x rows per batch); else 2 rows (hi, lo) per batch
+__host__ __device__ inline SmemPlan make_plan(int ng, int stages, int max_slice_segs, int M, int MB, int aux_per_seg, int pairs) {
+  SmemPlan p;
+  p.stages = stages;
+  p.x_stride = max_slice_segs * 256 + (pairs ? 16 : 32);
+  p.aux_stride = max_slice_segs * aux_per_seg + 4;
+  p.seg_stride = max_slice_segs;
+  p.off_ring = 0;
+  p.off_x = ng * kGroupWarps * stages * kStageBytes;
+  p.off_aux = p.off_x + (pairs ? 8 : 2) * M * p.x_stride;
+  p.off_delta = p.off_aux + M * p.aux_stride * 4;
+  p.off_slots = (p.off_delta + M * p.seg_stride * 4 + 15) & ~15;
+  p.off_tile = p.off_slots + ng * kSlots * kGroupWarps * kTileRows * MB * 4;
+  p.off_misc = p.off_tile + ng * kSlots * kTileRows * MB * 4;
+  p.off_misc = (p.off_misc + 15) & ~15;
+  p.off_misc = (p.off_misc + 127) & ~127;
+  p.total = p.off_misc + 1024;
+  return p;
+}
+
+struct Misc {
+  unsigned long long full[2 * kGroupWarps][kMaxStages];   // one mbarrier per compute warp and stage
+  float redbuf[32];
+  int dead;
+};
+static_assert(sizeof(Misc) <= 1024, "Misc must fit its smem slot");
 
 // ---- PTX wrappers ------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
@@ -95,96 +150,39 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait: false (and *dead set) when the limit is reached.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* dead) {
-  if (*dead) return false;
   for (uint32_t i = 0; i < kSpinLimit; i++)
     if (mbar_try_wait(bar, parity)) return true;
   *dead = 1;
   return false;
 }
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+// One box of the 2-D tensor map: x in 8-byte elements (even: 16-byte rule), y in rows.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+               ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
 }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory"); }
-
-__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+// Named barriers 1..15: arrive does not block, sync does; both order shared-memory accesses.
+__device__ __forceinline__ void bar_arrive(int id, int nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+__device__ __forceinline__ void bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+// The MMAs are pure functions of their register operands: not volatile, so the compiler may
+// schedule them among the loads and the logic of neighbouring sub-blocks.
+__device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void mma1688(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
-               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-               : "r"(a0), "r"(a1), "r"(b0));
+  asm("mma.sync.aligned.m16n8k8.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(b0));
 }
-__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
-  uint32_t r;
-  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));  // (a & b) | c
-  return r;
+__device__ __forceinline__ uint32_t pack_half2(__half lo, __half hi) {
+  return (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16);
 }
-__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
-}
-
-// 8 nibbles of one 32-bit word -> four half2 registers holding (q - 8) exactly:
-// out[0] = (n0, n4), out[1] = (n1, n5), out[2] = (n2, n6), out[3] = (n3, n7).
-__device__ __forceinline__ void nibbles_to_half2(uint32_t w, uint32_t (&out)[4]) {
-  const uint32_t ws = w >> 8;
-  out[0] = hsub2_u32(lop3_and_or(w, 0x000f000fu, 0x64006400u), 0x64086408u);   // 1024 + q - 1032
-  out[1] = hsub2_u32(lop3_and_or(w, 0x00f000f0u, 0x54005400u), 0x54805480u);   // 64 + q - 72
-  out[2] = hsub2_u32(lop3_and_or(ws, 0x000f000fu, 0x64006400u), 0x64086408u);
-  out[3] = hsub2_u32(lop3_and_or(ws, 0x00f000f0u, 0x54005400u), 0x54805480u);
-}
-
-// position of element e (0..7) of an 8-group in the permuted x layout (0,4,1,5,2,6,3,7)
-__host__ __device__ inline int perm8(int e) { return ((e & 3) << 1) | (e >> 2); }
-
-// Shared-memory plan (bytes), identical on host and device.
-struct SmemPlan {
-  int stages;
-  int x_stride;      // bytes per batch column of the fp16 x slice
-  int sxp_stride;    // words per batch column of the pair-sum table
-  int off_ring, off_x, off_sxp, off_red, off_tile, off_misc, total;
-};
-__host__ __device__ inline SmemPlan make_plan(int stages, int max_slice_k, int max_slice_segs, int mcols, int xcols) {
-  SmemPlan p;
-  p.stages = stages;
-  p.x_stride = max_slice_k * 2 + 64;
-  int w = max_slice_segs * 4;
-  p.sxp_stride = w + ((4 - (w & 31)) & 31);          // = 4 (mod 32)
-  p.off_ring = 0;
-  p.off_x = p.off_ring + stages * kStageBytes;
-  p.off_sxp = p.off_x + xcols * p.x_stride;
-  p.off_red = p.off_sxp + xcols * p.sxp_stride * 4;
-  p.off_tile = p.off_red + kConsumerWarps * kTileRows * mcols * 4;
-  p.off_misc = p.off_tile + kTileRows * mcols * 4;
-  p.total = p.off_misc + 1024;
-  return p;
-}
-
-struct Misc {
-  unsigned long long full[16];
-  unsigned long long empty[16];
-  float colscale[16];    // 2^e per batch column (x16 = x * 2^-e)
-  float colrinv[16];
-  float redbuf[kConsumerWarps * 16];
-  int dead;
-  int last_flag;
-};
-static_assert(sizeof(Misc) <= 1024, "Misc must fit its smem slot");
 
 __device__ __forceinline__ int slice_segs(const Phase& ph, int ks) { return ph.segs_base + (ks < ph.segs_extra ? 1 : 0); }
 __device__ __forceinline__ int slice_seg0(const Phase& ph, int ks) {
@@ -205,386 +203,722 @@ __device__ __forceinline__ const uint8_t* tile_row(const Phase& ph, int t, int r
   return ph.w[m] + (size_t)R * ph.row_bytes;
 }
 
-template <int QT, typename T, int NT>
-__global__ void __launch_bounds__(kThreads, 1) decode_kernel(const __grid_constant__ Params P, const __grid_constant__ SmemPlan plan) {
+// Tiles of one (CTA, group) in a phase: t = first + i * step, i = 0 .. count-1.  The CTA
+// works on K-slice cta % S; the gridDim.x / S CTAs of a slice, times NG groups, share the tiles.
+struct TileLane { int first, step, count; };
+__device__ __forceinline__ TileLane tile_lane(const Phase& ph, int cta, int G, int group, int ng) {
+  TileLane tl;
+  tl.step = (G / ph.S) * ng;
+  tl.first = (cta / ph.S) * ng + group;
+  tl.count = tl.first < ph.ntiles ? (ph.ntiles - 1 - tl.first) / tl.step + 1 : 0;
+  return tl;
+}
+
+// Eight consecutive activations -> fp32 (16-byte vector loads when aligned), L2-coherent.
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&v)[8]) {
+  if constexpr (sizeof(T) == 2) {
+    if ((reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+      const uint4 u = __ldcg(reinterpret_cast<const uint4*>(p));
+      const T* h = reinterpret_cast<const T*>(&u);
+#pragma unroll
+      for (int i = 0; i < 8; i++) v[i] = Act<T>::to_f(h[i]);
+      return;
+    }
+  } else {
+    if ((reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+      const float4 a = __ldcg(reinterpret_cast<const float4*>(p)), b = __ldcg(reinterpret_cast<const float4*>(p) + 1);
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+      return;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; i++) v[i] = Act<T>::to_f(__ldcg(p + i));
+}
+
+// ---- x prologue --------------------------------------------------------------------------
+// The CTA's K-slice of x -> [RMSNorm, round to T] -> 16-bit fixed point per 256-element
+// segment, stored as hi / lo signed bytes in MMA k order, plus the per-segment scale and the
+// per-sub-block sums the offset / min term needs.  One warp per segment, 8 consecutive
+// elements per lane; with a segment per warp the slice is read from L2 exactly once.
+// PAIRS: layout of the batch <= 2 mapping (see segment_mma_pairs): per batch eight rows
+// (pair p, part), row (p, part) holding x only inside the sub-blocks of pair p, and the sums
+// as plain floats.  pre / gpre: x and gamma of (batch 0, segment = warp) loaded by the caller
+// before it queued the weight prefetch (loads issued later wait behind it in the LSU).
+template <int QT, typename T, bool PAIRS>
+__device__ __forceinline__ void x_prologue(const Phase& ph, const SmemPlan& plan, uint8_t* smem, Misc* misc,
+                                           int M, int nseg, int seg0, int nwarps, bool have_pre,
+                                           const float (&pre)[8], const float (&gpre)[8], unsigned long long* tr) {
+  auto tstamp = [&](int i) { if (tr && threadIdx.x == 0) { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); tr[i] = t; } };
+  constexpr int AUXW = (QT == MLXR_Q4_K) ? 4 : 8;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int k0 = seg0 * 256;
+  const T* xg = reinterpret_cast<const T*>(ph.x);
+  const T* gam = reinterpret_cast<const T*>(ph.gamma);
+  uint32_t* aux = reinterpret_cast<uint32_t*>(smem + plan.off_aux);
+  float* delta = reinterpret_cast<float*>(smem + plan.off_delta);
+  const bool whole_row = (nseg * 256 == ph.K);
+  for (int m = 0; m < M; m++) {
+    const T* xrow_g = xg + (size_t)m * ph.K;
+    float v0[8];            // first segment of this warp, kept across the reduction
+    bool have0 = false;
+    const bool use_pre = have_pre && m == 0 && warp < nseg;
+    if (use_pre) {
+#pragma unroll
+      for (int i = 0; i < 8; i++) v0[i] = pre[i];
+      have0 = true;
+    }
+    float rinv = 1.0f;
+    if (gam) {
+      float ss = 0.0f;
+      if (whole_row) {
+        for (int sg = warp; sg < nseg; sg += nwarps) {
+          float v[8];
+          if (use_pre && sg == warp) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = v0[i];
+          } else {
+            load8(xrow_g + sg * 256 + lane * 8, v);
+          }
+#pragma unroll
+          for (int i = 0; i < 8; i++) ss = fmaf(v[i], v[i], ss);
+          if (sg == warp) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) v0[i] = v[i];
+            have0 = true;
+          }
+        }
+      } else {
+        for (int k = tid * 8; k < ph.K; k += blockDim.x * 8) {
+          float v[8];
+          load8(xrow_g + k, v);
+#pragma unroll
+          for (int i = 0; i < 8; i++) ss = fmaf(v[i], v[i], ss);
+        }
+      }
+      ss = warp_sum(ss);
+      if (lane == 0) misc->redbuf[warp] = ss;
+      __syncthreads();
+      float tot = 0.0f;
+      for (int i = 0; i < nwarps; i++) tot += misc->redbuf[i];
+      rinv = 1.0f / sqrtf(tot / (float)ph.K + ph.eps);
+      __syncthreads();
+    }
+    for (int sg = warp; sg < nseg; sg += nwarps) {
+      float v[8];
+      if (have0 && sg == warp) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = v0[i];
+      } else {
+        load8(xrow_g + k0 + sg * 256 + lane * 8, v);
+      }
+      if (gam) {
+        float gv[8];
+        if (use_pre && sg == warp) {
+#pragma unroll
+          for (int i = 0; i < 8; i++) gv[i] = gpre[i];
+        } else {
+          load8(gam + k0 + sg * 256 + lane * 8, gv);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = Act<T>::to_f(Act<T>::from_f(__fmul_rn(__fmul_rn(v[i], rinv), gv[i])));
+      }
+      float amax = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      // x ~ dl * xi with |xi| <= 32000; a non-finite block poisons its outputs with NaN
+      float dl = 1.0f, inv = 0.0f;
+      if (!(amax <= 3.0e38f)) { dl = __int_as_float(0x7fc00000); }
+      else if (amax > 0.0f) { dl = amax * (1.0f / 32000.0f); inv = 32000.0f / amax; }
+      int ssum = 0;
+      uint32_t hi_e = 0, hi_o = 0, lo_e = 0, lo_o = 0;
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        int q16 = __float2int_rn(v[i] * inv);
+        q16 = max(-32000, min(32000, q16));
+        ssum += q16;
+        const int h8 = (q16 + 128) >> 8, l8 = q16 - (h8 << 8);   // q16 = 256*h8 + l8, both in [-128,127]
+        const uint32_t hb = (uint32_t)(h8 & 0xFF), lb = (uint32_t)(l8 & 0xFF);
+        if (i & 1) { hi_o |= hb << (8 * (i >> 1)); lo_o |= lb << (8 * (i >> 1)); }
+        else       { hi_e |= hb << (8 * (i >> 1)); lo_e |= lb << (8 * (i >> 1)); }
+      }
+      // bytes of an 8-group are stored as (e0,e2,e4,e6 | e1,e3,e5,e7): the MMA k order
+      if constexpr (PAIRS) {
+        // sub-block lane/4 belongs to pair {0,1,0,0,2,3,2,2}[lane/4]; the other pairs' rows get zeros
+        const int myp = (0x22320010u >> (4 * (lane >> 2))) & 7;
+        uint8_t* xrow = smem + plan.off_x + (size_t)(8 * m) * plan.x_stride + sg * 256 + lane * 8;
+#pragma unroll
+        for (int p4 = 0; p4 < 4; p4++) {
+          const bool mine = p4 == myp;
+          *reinterpret_cast<uint2*>(xrow + (size_t)(2 * p4) * plan.x_stride) = mine ? make_uint2(hi_e, hi_o) : make_uint2(0u, 0u);
+          *reinterpret_cast<uint2*>(xrow + (size_t)(2 * p4 + 1) * plan.x_stride) = mine ? make_uint2(lo_e, lo_o) : make_uint2(0u, 0u);
+        }
+      } else {
+        uint8_t* xrow = smem + plan.off_x + (size_t)(2 * m) * plan.x_stride + sg * 256 + lane * 8;
+        *reinterpret_cast<uint2*>(xrow) = make_uint2(hi_e, hi_o);
+        *reinterpret_cast<uint2*>(xrow + plan.x_stride) = make_uint2(lo_e, lo_o);
+      }
+      // sums of xi per 32-element sub-block (4 lanes each)
+      ssum += __shfl_xor_sync(0xffffffffu, ssum, 1);
+      ssum += __shfl_xor_sync(0xffffffffu, ssum, 2);
+      int sb[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) sb[j] = __shfl_sync(0xffffffffu, ssum, 4 * j);
+      if (lane == 0) delta[m * plan.seg_stride + sg] = dl;
+      uint32_t* arow = aux + (size_t)m * plan.aux_stride + sg * AUXW;
+      if (lane < 4) {
+        if constexpr (PAIRS) {
+          // exact integer sums over the sub-blocks of each (scale, min) pair, as floats
+          const int ps = lane == 0 ? sb[0] + sb[2] + sb[3] : lane == 1 ? sb[1] : lane == 2 ? sb[4] + sb[6] + sb[7] : sb[5];
+          arow[lane] = __float_as_uint((float)ps);
+        } else if constexpr (QT == MLXR_Q4_K) {
+          // sums over the sub-blocks that share a (scale, min) pair, in units of 2^10
+          const int ps = lane == 0 ? sb[0] + sb[2] + sb[3] : lane == 1 ? sb[1] : lane == 2 ? sb[4] + sb[6] + sb[7] : sb[5];
+          const float f = (float)ps * (1.0f / 1024.0f);
+          const __half h = __float2half_rn(f);
+          arow[lane] = pack_half2(h, __float2half_rn(f - __half2float(h)));
+        } else {
+          // -8 * sum per sub-block in units of 2^10: word j = sub-blocks (2j, 2j+1); hi words, then lo words
+          const int a = lane == 0 ? sb[0] : lane == 1 ? sb[2] : lane == 2 ? sb[4] : sb[6];
+          const int b = lane == 0 ? sb[1] : lane == 1 ? sb[3] : lane == 2 ? sb[5] : sb[7];
+          const float fa = (float)a * (-8.0f / 1024.0f), fb = (float)b * (-8.0f / 1024.0f);
+          const __half ha = __float2half_rn(fa), hb2 = __float2half_rn(fb);
+          arow[lane] = pack_half2(ha, hb2);
+          arow[4 + lane] = pack_half2(__float2half_rn(fa - __half2float(ha)), __float2half_rn(fb - __half2float(hb2)));
+        }
+      }
+    }
+  }
+}
+
+// ---- one 256-element segment of 16 rows ---------------------------------------------------
+// rl / rh: this thread's two rows (g and g+8) of the stage, at the segment's first byte.
+// xb[j]: this thread's B-fragment bytes of n-tile j for the segment (null when the MMA column
+// has no batch row behind it); auxp[j]: its word of the sum table (null likewise);
+// dl[j]: fixed-point scale of batch column c + 4j for this segment.
+template <int QT, int NT>
+__device__ __forceinline__ void segment_mma(const uint8_t* rl, const uint8_t* rh, const uint8_t* const (&xb)[NT],
+                                            const uint32_t* const (&auxp)[NT], const float (&dl)[NT], int lane,
+                                            float (&total)[NT][2]) {
+  const int c = lane & 3;
+  float segacc[NT][2];
+  float minacc[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; j++) {
+    segacc[j][0] = segacc[j][1] = 0.0f;
+    minacc[j][0] = minacc[j][1] = minacc[j][2] = minacc[j][3] = 0.0f;
+  }
+  if constexpr (QT == MLXR_Q4_K) {
+    const uint4 hl = *reinterpret_cast<const uint4*>(rl), hh = *reinterpret_cast<const uint4*>(rh);
+    // this thread decodes (scale, min) pair c of both rows (q_gemm_dequant.metal:222-242, fields
+    // read straight from the packed words); the quad shares the four scales by shuffle
+    float ssl[4], ssh[4];
+    uint32_t amin_lo, amin_hi;
+    {
+      const __half2 dl2 = *reinterpret_cast<const __half2*>(&hl.x), dh2 = *reinterpret_cast<const __half2*>(&hh.x);
+      const uint32_t w2 = hl.y, w3 = hl.z, v2 = hh.y, v3 = hh.z;
+      const uint32_t scl = c == 0 ? w2 : c == 1 ? (w2 >> 12) : c == 2 ? (w2 >> 24) : (w3 >> 4);
+      const uint32_t sch = c == 0 ? v2 : c == 1 ? (v2 >> 12) : c == 2 ? (v2 >> 24) : (v3 >> 4);
+      const uint32_t mnl = c == 0 ? (w2 >> 6) : c == 1 ? (w2 >> 18) : c == 2 ? ((w2 >> 30) | ((w3 & 15u) << 2)) : (w3 >> 10);
+      const uint32_t mnh = c == 0 ? (v2 >> 6) : c == 1 ? (v2 >> 18) : c == 2 ? ((v2 >> 30) | ((v3 & 15u) << 2)) : (v3 >> 10);
+      const float my_sl = __half2float(__hmul(__int2half_rn((int)(scl & 63u)), __low2half(dl2)));
+      const float my_sh = __half2float(__hmul(__int2half_rn((int)(sch & 63u)), __low2half(dh2)));
+      const float my_ml = __half2float(__hmul(__int2half_rn((int)(mnl & 63u)), __high2half(dl2)));
+      const float my_mh = __half2float(__hmul(__int2half_rn((int)(mnh & 63u)), __high2half(dh2)));
+      // w = (q - 8) * ss + sm = q * ss + (sm - 8 ss): the second term times sum(x)
+      const __half ol = __float2half_rn(fmaf(-8.0f, my_sl, my_ml));
+      const __half oh = __float2half_rn(fmaf(-8.0f, my_sh, my_mh));
+      amin_lo = pack_half2(ol, ol);
+      amin_hi = pack_half2(oh, oh);
+#pragma unroll
+      for (int p = 0; p < 4; p++) {
+        ssl[p] = __shfl_sync(0xffffffffu, my_sl, (lane & ~3) | p);
+        ssh[p] = __shfl_sync(0xffffffffu, my_sh, (lane & ~3) | p);
+      }
+    }
+    // sub-blocks in the order that keeps those sharing a (scale, min) pair together
+    constexpr int order[8] = {0, 2, 3, 1, 4, 6, 7, 5};
+    constexpr int pair_of[8] = {0, 0, 0, 1, 2, 2, 2, 3};
+    constexpr bool last_of_pair[8] = {false, false, true, true, false, false, true, true};
+    const uint32_t* ql = reinterpret_cast<const uint32_t*>(rl + 16) + c;
+    const uint32_t* qh = reinterpret_cast<const uint32_t*>(rh + 16) + c;
+    uint32_t wl[8], wh[8];
+#pragma unroll
+    for (int s = 0; s < 8; s++) { wl[s] = ql[4 * s]; wh[s] = qh[4 * s]; }
+    int acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const int s = order[i];
+      // even nibbles (elements 8c+0,2,4,6) and odd nibbles (8c+1,3,5,7) as u8x4
+      const uint32_t a0 = wl[s] & 0x0f0f0f0fu, a2 = (wl[s] >> 4) & 0x0f0f0f0fu;
+      const uint32_t a1 = wh[s] & 0x0f0f0f0fu, a3 = (wh[s] >> 4) & 0x0f0f0f0fu;
+#pragma unroll
+      for (int j = 0; j < NT; j++) {
+        uint2 b = make_uint2(0u, 0u);
+        if (xb[j]) b = *reinterpret_cast<const uint2*>(xb[j] + 32 * s);
+        imma16832(acc[j], a0, a1, a2, a3, b.x, b.y);
+      }
+      if (last_of_pair[i]) {
+        const int p = pair_of[i];
+#pragma unroll
+        for (int j = 0; j < NT; j++) {
+          // columns 2c, 2c+1 of this thread = hi and lo byte sums of batch c (+4j)
+          segacc[j][0] = fmaf(ssl[p], (float)(acc[j][0] * 256 + acc[j][1]), segacc[j][0]);
+          segacc[j][1] = fmaf(ssh[p], (float)(acc[j][2] * 256 + acc[j][3]), segacc[j][1]);
+          acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0;
+        }
+      }
+    }
+    // offset + min term: sum_p (sm_p - 8 ss_p) * Sx_p, Sx_p as hi + lo halves in column 2*batch
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+      const uint32_t b = auxp[j] ? auxp[j][c] : 0u;
+      mma1688(minacc[j], amin_lo, amin_hi, b);
+    }
+  } else {  // Q4_0: 8 blocks of 18 B; scale at +18s, nibbles at +18s+2
+    const uint16_t* hl16 = reinterpret_cast<const uint16_t*>(rl);
+    const uint16_t* hh16 = reinterpret_cast<const uint16_t*>(rh);
+#pragma unroll
+    for (int s = 0; s < 8; s++) {
+      uint32_t wl, wh;
+      if (s & 1) {  // 18s+2 is 4-byte aligned
+        wl = *reinterpret_cast<const uint32_t*>(rl + 18 * s + 2 + 4 * c);
+        wh = *reinterpret_cast<const uint32_t*>(rh + 18 * s + 2 + 4 * c);
+      } else {      // straddles two words
+        const uint32_t* pl = reinterpret_cast<const uint32_t*>(rl + 18 * s + 4 * c);
+        const uint32_t* ph = reinterpret_cast<const uint32_t*>(rh + 18 * s + 4 * c);
+        wl = __funnelshift_r(pl[0], pl[1], 16);
+        wh = __funnelshift_r(ph[0], ph[1], 16);
+      }
+      const float fl = __half2float(__ushort_as_half(hl16[9 * s]));
+      const float fh = __half2float(__ushort_as_half(hh16[9 * s]));
+      const uint32_t a0 = wl & 0x0f0f0f0fu, a2 = (wl >> 4) & 0x0f0f0f0fu;
+      const uint32_t a1 = wh & 0x0f0f0f0fu, a3 = (wh >> 4) & 0x0f0f0f0fu;
+#pragma unroll
+      for (int j = 0; j < NT; j++) {
+        int acc[4] = {0, 0, 0, 0};
+        uint2 b = make_uint2(0u, 0u);
+        if (xb[j]) b = *reinterpret_cast<const uint2*>(xb[j] + 32 * s);
+        imma16832(acc, a0, a1, a2, a3, b.x, b.y);
+        segacc[j][0] = fmaf(fl, (float)(acc[0] * 256 + acc[1]), segacc[j][0]);
+        segacc[j][1] = fmaf(fh, (float)(acc[2] * 256 + acc[3]), segacc[j][1]);
+      }
+    }
+    // -8 * sum_s d_s * Sx_s: A = the scales of sub-blocks 2c, 2c+1 (exact in half)
+    const uint32_t al = (uint32_t)hl16[18 * c] | ((uint32_t)hl16[18 * c + 9] << 16);
+    const uint32_t ah = (uint32_t)hh16[18 * c] | ((uint32_t)hh16[18 * c + 9] << 16);
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+      const uint32_t bh = auxp[j] ? auxp[j][c] : 0u, bl = auxp[j] ? auxp[j][4 + c] : 0u;
+      mma1688(minacc[j], al, ah, bh);
+      mma1688(minacc[j], al, ah, bl);
+    }
+  }
+  // fold the segment: units are delta (per batch column and segment)
+#pragma unroll
+  for (int j = 0; j < NT; j++) {
+    total[j][0] = fmaf(dl[j], fmaf(1024.0f, minacc[j][0], segacc[j][0]), total[j][0]);
+    total[j][1] = fmaf(dl[j], fmaf(1024.0f, minacc[j][2], segacc[j][1]), total[j][1]);
+  }
+}
+
+// ---- the same for batch <= 2: pairs in the MMA columns (Q4_K) -----------------------------------
+// MMA column 2p + part of n-tile j holds batch j's x restricted to the sub-blocks of (scale, min)
+// pair p (four masked copies of x in shared memory), so one accumulation runs over the whole
+// 256-block with no reset, and thread (g, c) ends up with the hi / lo sums of pair c for rows g
+// and g+8: it scales them with the pair it decoded itself -- no shuffles.  Because the masks
+// live in the data, one MMA may mix sub-blocks: thread c feeds words of sub-block c (then 4+c),
+// which lets weights and x come in 128-bit loads (12 shared loads per segment instead of 29).
+// The four threads of a quad hold different pairs' partial sums; the epilogue warp adds them.
+// x0: this lane's x row (g) of batch 0 at the segment, + 32 c; sx0: pair sums of batch 0 at the
+// segment, + c; dl0: delta of batch 0 at the segment.
+template <int NT>
+__device__ __forceinline__ void segment_mma_pairs(const uint8_t* rl, const uint8_t* rh, const uint8_t* x0, int x_batch_stride,
+                                                  const float* sx0, int aux_stride, const float* dl0, int seg_stride,
+                                                  int c, int sh1, int sh2, float (&total)[NT][2]) {
+  const uint4 hl = *reinterpret_cast<const uint4*>(rl), hh = *reinterpret_cast<const uint4*>(rh);
+  uint4 wl[2], wh[2];
+  wl[0] = *reinterpret_cast<const uint4*>(rl + 16 + 16 * c);
+  wl[1] = *reinterpret_cast<const uint4*>(rl + 80 + 16 * c);
+  wh[0] = *reinterpret_cast<const uint4*>(rh + 16 + 16 * c);
+  wh[1] = *reinterpret_cast<const uint4*>(rh + 80 + 16 * c);
+  int acc[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0;
+#pragma unroll
+  for (int h = 0; h < 2; h++) {
+    uint4 xa[NT], xb[NT];
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+      xa[j] = *reinterpret_cast<const uint4*>(x0 + (size_t)j * x_batch_stride + 128 * h);
+      xb[j] = *reinterpret_cast<const uint4*>(x0 + (size_t)j * x_batch_stride + 128 * h + 16);
+    }
+    const uint32_t wlw[4] = {wl[h].x, wl[h].y, wl[h].z, wl[h].w}, whw[4] = {wh[h].x, wh[h].y, wh[h].z, wh[h].w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const uint32_t a0 = wlw[i] & 0x0f0f0f0fu, a2 = (wlw[i] >> 4) & 0x0f0f0f0fu;
+      const uint32_t a1 = whw[i] & 0x0f0f0f0fu, a3 = (whw[i] >> 4) & 0x0f0f0f0fu;
+#pragma unroll
+      for (int j = 0; j < NT; j++) {
+        const uint32_t b0 = i == 0 ? xa[j].x : i == 1 ? xa[j].z : i == 2 ? xb[j].x : xb[j].z;
+        const uint32_t b1 = i == 0 ? xa[j].y : i == 1 ? xa[j].w : i == 2 ? xb[j].y : xb[j].w;
+        imma16832(acc[j], a0, a1, a2, a3, b0, b1);
+      }
+    }
+  }
+  // (scale, min) pair c of both rows: 6-bit fields at bit 12c (scale) and 12c + 6 (min) of the
+  // 48 packed bits scales[0..5] (q_gemm_dequant.metal:222-242)
+  const uint32_t ul = __funnelshift_r(hl.y, hl.z, sh1) >> sh2, uh = __funnelshift_r(hh.y, hh.z, sh1) >> sh2;
+  const __half2 dl2 = *reinterpret_cast<const __half2*>(&hl.x), dh2 = *reinterpret_cast<const __half2*>(&hh.x);
+  const float ss_l = __half2float(__hmul(__int2half_rn((int)(ul & 63u)), __low2half(dl2)));
+  const float ss_h = __half2float(__hmul(__int2half_rn((int)(uh & 63u)), __low2half(dh2)));
+  const float sm_l = __half2float(__hmul(__int2half_rn((int)((ul >> 6) & 63u)), __high2half(dl2)));
+  const float sm_h = __half2float(__hmul(__int2half_rn((int)((uh >> 6) & 63u)), __high2half(dh2)));
+  // w = (q - 8) * ss + sm = q * ss + (sm - 8 ss); the second term multiplies sum(x) of the pair
+  const float of_l = fmaf(-8.0f, ss_l, sm_l), of_h = fmaf(-8.0f, ss_h, sm_h);
+#pragma unroll
+  for (int j = 0; j < NT; j++) {
+    const float sx = sx0[(size_t)j * aux_stride];
+    const float dl = dl0[(size_t)j * seg_stride];
+    const float v0 = (float)(acc[j][0] * 256 + acc[j][1]), v1 = (float)(acc[j][2] * 256 + acc[j][3]);
+    total[j][0] = fmaf(dl, fmaf(ss_l, v0, of_l * sx), total[j][0]);
+    total[j][1] = fmaf(dl, fmaf(ss_h, v1, of_h * sx), total[j][1]);
+  }
+}
+
+// ---- tile epilogue (one warp) --------------------------------------------------------------
+// tile[row][col] holds the complete sums of this CTA's K-slice for 16 rows x MB batch columns.
+template <typename T, int MB>
+__device__ __forceinline__ void tile_epilogue(const Params& P, const Phase& ph, float* tile, int t, int ks, int lane) {
+  const int M = P.M;
+  bool do_epilogue = true;
+  if (ph.S > 1) {
+    // split-K over CTAs: park the partial; the last slice to arrive reduces all of them
+    const size_t slab = (size_t)ph.ntiles * kTileRows * MB;
+    float* gm = ph.partials + (size_t)ks * slab + (size_t)t * kTileRows * MB;
+    for (int e = lane; e < kTileRows * MB; e += 32) __stcg(&gm[e], tile[e]);
+    __threadfence();
+    __syncwarp();
+    int lastk = 0;
+    if (lane == 0) {
+      const uint32_t prev = atomicAdd(&ph.counters[t], 1u);
+      lastk = (prev == (uint32_t)ph.S - 1u);
+      if (lastk) ph.counters[t] = 0u;   // self-cleaning for the next launch
+      __threadfence();
+    }
+    lastk = __shfl_sync(0xffffffffu, lastk, 0);
+    do_epilogue = lastk != 0;
+    if (do_epilogue) {
+      for (int e = lane; e < kTileRows * MB; e += 32) {
+        float v = 0.0f;
+        for (int s2 = 0; s2 < ph.S; s2++) v += __ldcg(&ph.partials[(size_t)s2 * slab + (size_t)t * kTileRows * MB + e]);
+        tile[e] = v;
+      }
+      __syncwarp();
+    }
+  }
+  if (!do_epilogue) return;
+  if (ph.interleave) {
+    // rows 0..7 gate, 8..15 up of the same 8 intermediate indices: h = SiLU(g) * u
+    for (int e = lane; e < 8 * MB; e += 32) {
+      const int r = e / MB, m = e % MB;
+      const int col = 8 * t + r;
+      if (m < M && col < ph.n_total) {
+        const float gv = Act<T>::to_f(Act<T>::from_f(tile[r * MB + m]));
+        const float uv = Act<T>::to_f(Act<T>::from_f(tile[(r + 8) * MB + m]));
+        reinterpret_cast<T*>(ph.y[0])[(size_t)m * ph.n_total + col] = Act<T>::from_f(swish_f(gv) * uv);
+      }
+    }
+  } else {
+    // pairs of adjacent rows (2j, 2j+1): plain store or RoPE rotation
+    for (int e = lane; e < 8 * MB; e += 32) {
+      const int jj = e / MB, m = e % MB;
+      int R = kTileRows * t + 2 * jj;
+      if (m >= M || R >= ph.n_total) continue;
+      int mat = 0;
+      if (ph.nmat > 1 && R >= ph.rows[0]) { R -= ph.rows[0]; mat = 1; if (ph.nmat > 2 && R >= ph.rows[1]) { R -= ph.rows[1]; mat = 2; } }
+      const bool has_odd = R + 1 < ph.rows[mat];
+      float ve = tile[(2 * jj) * MB + m], vo = tile[(2 * jj + 1) * MB + m];
+      const T* bias = reinterpret_cast<const T*>(ph.bias[mat]);
+      if (bias) { ve += Act<T>::to_f(bias[R]); if (has_odd) vo += Act<T>::to_f(bias[R + 1]); }
+      T* out = reinterpret_cast<T*>(ph.y[mat]) + (size_t)m * ph.rows[mat] + R;
+      if (ph.epi[mat] == kEpiRope) {
+        const float qe = Act<T>::to_f(Act<T>::from_f(ve)), qo = Act<T>::to_f(Act<T>::from_f(vo));
+        const long long pos = (long long)ph.positions[m] + ph.pos_offset;
+        if (pos < 0 || pos >= ph.max_seq) { atomicExch(P.status, MLXR_ERR_SHAPE); continue; }
+        const int pairs = ph.head_dim >> 1, pi = (R % ph.head_dim) >> 1;
+        const float cs = __half2float(ph.cos_t[(size_t)pos * pairs + pi]);
+        const float sn = __half2float(ph.sin_t[(size_t)pos * pairs + pi]);
+        out[0] = Act<T>::from_f(__fsub_rn(__fmul_rn(qe, cs), __fmul_rn(qo, sn)));
+        out[1] = Act<T>::from_f(__fadd_rn(__fmul_rn(qo, cs), __fmul_rn(qe, sn)));
+      } else {
+        out[0] = Act<T>::from_f(ve);
+        if (has_odd) out[1] = Act<T>::from_f(vo);
+      }
+    }
+  }
+}
+
+// ---- the kernel ------------------------------------------------------------------------------
+// PAIRS: the batch <= 2 fragment mapping (Q4_K only, NT = batch); otherwise batch x {hi, lo}
+// in the MMA columns, four batch rows per n-tile.
+template <int QT, typename T, int NT, int NG, bool PAIRS>
+__global__ void __launch_bounds__(NG * kGroupWarps * 32, 1)
+decode_kernel(const __grid_constant__ Params P, const __grid_constant__ SmemPlan plan) {
   extern __shared__ __align__(128) uint8_t smem[];
-  constexpr int MC = 8 * NT;  // batch columns held
+  constexpr int MB = 4 * NT;                       // batch columns held (two MMA columns each)
+  constexpr int AUXW = (QT == MLXR_Q4_K) ? 4 : 8;
+  constexpr int kComputeWarps = NG * kGroupWarps;
+  constexpr int kAllWarps = kComputeWarps;
+  constexpr int kFullThreads = kGroupWarps * 32;        // seven arrive + the duty warp syncs
+  constexpr int kFreeThreads = (kGroupWarps + 1) * 32;  // eight writers sync + the duty warp's earlier arrive
   Misc* misc = reinterpret_cast<Misc*>(smem + plan.off_misc);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, c = lane & 3;
+  // MMA row g is fed from tile row rg = g with its two low bits swapped: the two row groups of a
+  // quarter warp then sit 2 rows = 576 bytes = 16 banks apart in the dense TMA box, which makes
+  // the 128-bit weight loads conflict-free (adjacent rows, 288 bytes apart, would collide)
+  const int rg = (g & 4) | ((g & 1) << 1) | ((g >> 1) & 1);
   const int G = gridDim.x, cta = blockIdx.x;
   const int M = P.M;
-  volatile int* dead = &misc->dead;
+  const int D = plan.stages;
+  const int group = warp / kGroupWarps;
+  const int wg = warp % kGroupWarps;               // compute warp's index in its group
+  const int bar_full0 = 1 + group * 2 * kSlots, bar_free0 = bar_full0 + kSlots;
 
   if (tid == 0) {
     misc->dead = 0;
-    for (int s = 0; s < plan.stages; s++) {
-      mbar_init(smem_u32(&misc->full[s]), 1);
-      mbar_init(smem_u32(&misc->empty[s]), kConsumerWarps);
-    }
+    for (int w = 0; w < kComputeWarps; w++)
+      for (int st = 0; st < D; st++) mbar_init(smem_u32(&misc->full[w][st]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   __syncthreads();
+  auto stamp = [&](int i) {
+    if (P.trace && tid == 0) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+      P.trace[(size_t)cta * 16 + i] = t;
+    }
+  };
+  stamp(0);
 
-  const uint32_t ring = smem_u32(smem + plan.off_ring);
+  float* slots = reinterpret_cast<float*>(smem + plan.off_slots) + (size_t)group * kSlots * kGroupWarps * kTileRows * MB;
+  float* tiles = reinterpret_cast<float*>(smem + plan.off_tile) + (size_t)group * kSlots * kTileRows * MB;
+  const uint32_t* aux = reinterpret_cast<const uint32_t*>(smem + plan.off_aux);
+  const float* delta = reinterpret_cast<const float*>(smem + plan.off_delta);
 
-  if (warp == kConsumerWarps) {
-    // ================= producer warp =================
-    uint32_t n = 0;  // chunks issued so far
-    for (int phs = 0; phs < P.nphases; phs++) {
-      const Phase& ph = P.ph[phs];
-      const int nitems = ph.ntiles * ph.S;
-      for (int item = cta; item < nitems; item += G) {
-        const int t = item / ph.S, ks = item - t * ph.S;
-        const int nseg = slice_segs(ph, ks), seg0 = slice_seg0(ph, ks);
-        const int nchunks = (nseg + kMaxChunkSegs - 1) / kMaxChunkSegs;
-        const int cb = nseg / nchunks, ce = nseg - cb * nchunks;   // balanced chunk sizes
-        const uint8_t* src = lane < kTileRows ? tile_row(ph, t, lane) + (size_t)seg0 * kSegBytes : nullptr;
-        int done = 0;
-        for (int ch = 0; ch < nchunks; ch++) {
-          const int csegs = cb + (ch < ce ? 1 : 0);
-          const int stage = n % plan.stages;
-          const uint32_t par = ((n / plan.stages) & 1) ^ 1;
-          const uint32_t fullb = smem_u32(&misc->full[stage]);
-          bool ok = true;
-          if (lane == 0) ok = mbar_wait(smem_u32(&misc->empty[stage]), par, dead);
-          ok = __shfl_sync(0xffffffffu, ok, 0);
-          if (ok) {
-            const uint32_t bytes = (uint32_t)csegs * kSegBytes;
-            if (lane == 0) mbar_arrive_expect_tx(fullb, bytes * kTileRows);
-            __syncwarp();
-            if (lane < kTileRows)
-              bulk_g2s(ring + stage * kStageBytes + lane * kRowStride, src + (size_t)done * kSegBytes, bytes, fullb);
-          }
-          done += csegs;
-          n++;
+  // tiles this group handles over the whole launch (slot hand-back is skipped at the end)
+  int total_q = 0;
+  for (int p = 0; p < P.nphases; p++) total_q += tile_lane(P.ph[p], cta, G, group, NG).count;
+
+  // ---- this compute warp's private copy stream: (phase, tile, chunk) in consumption order ----
+  const uint32_t ring = smem_u32(smem + plan.off_ring) + warp * D * kStageBytes;
+  const uint8_t* ring_g = smem + plan.off_ring + (size_t)warp * D * kStageBytes;
+  int i_phs = 0, i_tile = 0, i_ch = 0, i_nch = 0, i_seg_first = 0, i_nsw = 0;
+  TileLane i_tl = {0, 1, 0};
+  auto enter_phase = [&]() {   // first phase >= i_phs with work for this warp
+    while (i_phs < P.nphases) {
+      const Phase& ph = P.ph[i_phs];
+      const int ks = cta % ph.S, nseg = slice_segs(ph, ks);
+      const int s0 = (wg * nseg) / kGroupWarps, s1 = ((wg + 1) * nseg) / kGroupWarps;
+      i_nsw = s1 - s0;
+      i_seg_first = slice_seg0(ph, ks) + s0;
+      i_nch = (i_nsw + kStageSegs - 1) / kStageSegs;
+      i_tl = tile_lane(ph, cta, G, group, NG);
+      i_tile = 0;
+      i_ch = 0;
+      if (i_tl.count > 0 && i_nch > 0) return;
+      i_phs++;
+    }
+  };
+  uint32_t n_issued = 0, n_consumed = 0;
+  // One stage = two TMA boxes (rows 0-7 and 8-15 of the tile, 288 bytes wide) signalling the
+  // stage's mbarrier; issued by lane 0.  Rows past the end of a matrix and bytes past the end
+  // of a row are zero-filled by the TMA unit (and still counted in the transaction bytes).
+  auto issue = [&]() {
+    if (i_phs >= P.nphases) return;
+    const Phase& ph = P.ph[i_phs];
+    if (lane == 0) {
+      const int t = i_tl.first + i_tile * i_tl.step;
+      const int stage = n_issued % D;
+      const uint32_t bar = smem_u32(&misc->full[warp][stage]);
+      const uint32_t dst = ring + stage * kStageBytes;
+      const int x = (i_seg_first + i_ch * kStageSegs) * (kSegBytes / 8);
+      int m0 = 0, y0, m1, y1;
+      if (ph.interleave) { y0 = 8 * t; m1 = 1; y1 = 8 * t; }
+      else {
+        y0 = kTileRows * t; m1 = 0; y1 = y0 + 8;
+        // stacked matrices: row counts are multiples of 8, so a half tile never straddles two
+        if (ph.nmat > 1) {
+          if (y0 >= ph.rows[0]) { y0 -= ph.rows[0]; m0 = 1; if (ph.nmat > 2 && y0 >= ph.rows[1]) { y0 -= ph.rows[1]; m0 = 2; } }
+          if (y1 >= ph.rows[0]) { y1 -= ph.rows[0]; m1 = 1; if (ph.nmat > 2 && y1 >= ph.rows[1]) { y1 -= ph.rows[1]; m1 = 2; } }
         }
       }
+      mbar_arrive_expect_tx(bar, kStageBytes);
+      tma_load_2d(dst, &P.tmap[i_phs][m0], x, y0, bar);
+      tma_load_2d(dst + 8 * kRowStride, &P.tmap[i_phs][m1], x, y1, bar);
     }
-    // If a wait gave up, copies may still be in flight: give them a bounded time to land
-    // before the CTA's shared memory is released.
-    if (*dead && lane == 0) {
-      for (int s = 0; s < plan.stages; s++)
-        for (uint32_t i = 0; i < (1u << 16); i++)
-          if (mbar_try_wait(smem_u32(&misc->full[s]), 0) || mbar_try_wait(smem_u32(&misc->full[s]), 1)) break;
+    n_issued++;
+    if (++i_ch >= i_nch) {
+      i_ch = 0;
+      if (++i_tile >= i_tl.count) { i_phs++; enter_phase(); }
     }
-    return;
+  };
+  // x (and gamma) of batch 0 for this warp's first segment are requested up front so that
+  // their latency overlaps the set-up below
+  float pre[8] = {0, 0, 0, 0, 0, 0, 0, 0}, gpre[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  bool have_pre = false;
+  {
+    const Phase& ph0 = P.ph[0];
+    const int ks0 = cta % ph0.S, nseg0 = slice_segs(ph0, ks0);
+    if (warp < nseg0 && tile_lane(ph0, cta, G, 0, NG).count > 0) {
+      const size_t k = (size_t)(slice_seg0(ph0, ks0) + warp) * 256 + lane * 8;
+      load8(reinterpret_cast<const T*>(ph0.x) + k, pre);
+      if (ph0.gamma) load8(reinterpret_cast<const T*>(ph0.gamma) + k, gpre);
+    }
+    have_pre = true;
   }
+  enter_phase();
+  for (int i = 0; i < D; i++) issue();
+  const int sh1 = c < 2 ? 12 * c : 24, sh2 = c == 3 ? 12 : 0;   // bit position of (scale, min) pair c
 
-  // ================= consumer warps =================
-  const int g = lane >> 2, c = lane & 3;
-  uint8_t* xs = smem + plan.off_x;
-  uint32_t* sxp = reinterpret_cast<uint32_t*>(smem + plan.off_sxp);
-  float* red = reinterpret_cast<float*>(smem + plan.off_red);
-  float* tilebuf = reinterpret_cast<float*>(smem + plan.off_tile);
-  const int ctid = tid;  // 0..255
-  uint32_t n = 0;
+  int qg = 0;  // sequence number of the tile within this group (indexes the hand-over slots)
 
   for (int phs = 0; phs < P.nphases; phs++) {
     const Phase& ph = P.ph[phs];
-    const int nitems = ph.ntiles * ph.S;
-
     if (phs > 0) {
       // ---- grid barrier: every CTA has finished (and made visible) the previous phase ----
       __threadfence();
-      consumer_sync();
-      if (ctid == 0) {
+      __syncthreads();
+      if (tid == 0) {
         const uint32_t target = P.bar_base + (uint32_t)phs * (uint32_t)G;
         atomicAdd(P.gridbar, 1u);
         bool ok = false;
-        for (uint32_t i = 0; i < (kSpinLimit << 2) && !*dead; i++) {
+        for (uint32_t i = 0; i < kSpinLimit; i++) {
           const uint32_t v = *reinterpret_cast<volatile uint32_t*>(P.gridbar);
           if ((int32_t)(v - target) >= 0) { ok = true; break; }
-          __nanosleep(32);
+          __nanosleep(20);
         }
-        if (!ok) { *dead = 1; }
+        if (!ok) misc->dead = 1;
         __threadfence();
       }
-      consumer_sync();
+      __syncthreads();
     }
-    if (cta >= nitems) continue;  // nothing to do in this phase (uniform per CTA)
+    // group 0 owns the lowest tile of the CTA: no tile there means no work in this phase
+    if (tile_lane(ph, cta, G, 0, NG).count == 0) continue;   // uniform per CTA
 
-    // ---- x prologue: this CTA's K-slice of x -> fp16, normalised, permuted ----------------
-    const int ks_mine = cta % ph.S;   // G % S == 0, so every item of this CTA has this slice
-    const int nseg = slice_segs(ph, ks_mine), seg0 = slice_seg0(ph, ks_mine);
-    const int k0 = seg0 * 256, kn = nseg * 256;
-    const T* xg = reinterpret_cast<const T*>(ph.x);
-    const T* gam = reinterpret_cast<const T*>(ph.gamma);
-    if (ctid < MC) misc->colscale[ctid] = 1.0f;
-    consumer_sync();
-    for (int m = 0; m < M; m++) {
-      float rinv = 1.0f;
-      if (gam) {
-        float ss = 0.0f;
-        for (int k = ctid; k < ph.K; k += kConsumerWarps * 32) {
-          const float v = Act<T>::to_f(__ldcg(&xg[(size_t)m * ph.K + k]));
-          ss = fmaf(v, v, ss);
-        }
-        ss = warp_sum(ss);
-        if (lane == 0) misc->redbuf[warp] = ss;
-        consumer_sync();
-        float tot = 0.0f;
-#pragma unroll
-        for (int i = 0; i < kConsumerWarps; i++) tot += misc->redbuf[i];
-        rinv = 1.0f / sqrtf(tot / (float)ph.K + ph.eps);
-        consumer_sync();
-      }
-      // pass 1: values of the slice (rounded to the activation dtype) and their max
-      float amax = 0.0f;
-      for (int k = ctid; k < kn; k += kConsumerWarps * 32) {
-        float v = Act<T>::to_f(__ldcg(&xg[(size_t)m * ph.K + k0 + k]));
-        if (gam) v = Act<T>::to_f(Act<T>::from_f(__fmul_rn(__fmul_rn(v, rinv), Act<T>::to_f(gam[k0 + k]))));
-        amax = fmaxf(amax, fabsf(v));
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-      if (lane == 0) misc->redbuf[warp] = amax;
-      consumer_sync();
-      amax = 0.0f;
-#pragma unroll
-      for (int i = 0; i < kConsumerWarps; i++) amax = fmaxf(amax, misc->redbuf[i]);
-      // power of two that brings amax into [16, 32): sums of 96 values stay below 65504
-      int e = 0;
-      if (amax > 0.0f && amax < 3.0e38f) { (void)frexpf(amax, &e); e -= 5; }
-      const float down = ldexpf(1.0f, -e);
-      if (ctid == 0) misc->colscale[m] = ldexpf(1.0f, e);
-      // pass 2: store fp16(v * 2^-e) at the permuted position
-      __half* xcol = reinterpret_cast<__half*>(xs + (size_t)m * plan.x_stride);
-      for (int k = ctid; k < kn; k += kConsumerWarps * 32) {
-        float v = Act<T>::to_f(__ldcg(&xg[(size_t)m * ph.K + k0 + k]));
-        if (gam) v = Act<T>::to_f(Act<T>::from_f(__fmul_rn(__fmul_rn(v, rinv), Act<T>::to_f(gam[k0 + k]))));
-        xcol[(k & ~7) | perm8(k & 7)] = __float2half_rn(v * down);
-      }
-      consumer_sync();
-      // pair sums for the Q4_K min term: sub-blocks {0,2,3}, {1}, {4,6,7}, {5} of every segment
-      if constexpr (QT == MLXR_Q4_K) {
-        for (int task = ctid; task < nseg * 4; task += kConsumerWarps * 32) {
-          const int sg = task >> 2, p = task & 3;
-          const int subs[4][3] = {{0, 2, 3}, {1, -1, -1}, {4, 6, 7}, {5, -1, -1}};
-          float s = 0.0f;
-          for (int j = 0; j < 3; j++) {
-            const int sb = subs[p][j];
-            if (sb < 0) continue;
-            const __half* q = xcol + sg * 256 + sb * 32;
-            for (int i = 0; i < 32; i++) s += __half2float(q[i]);
-          }
-          const __half hi = __float2half_rn(s);
-          const __half lo = __float2half_rn(s - __half2float(hi));
-          sxp[(size_t)m * plan.sxp_stride + sg * 4 + p] = (uint32_t)__half_as_ushort(hi) | ((uint32_t)__half_as_ushort(lo) << 16);
-        }
-      }
-    }
-    consumer_sync();
+    const int ks = cta % ph.S;
+    const int nseg = slice_segs(ph, ks), seg0 = slice_seg0(ph, ks);
+    x_prologue<QT, T, PAIRS>(ph, plan, smem, misc, M, nseg, seg0, kAllWarps, have_pre && phs == 0, pre, gpre,
+                             (P.trace && phs == 0) ? P.trace + (size_t)cta * 16 : nullptr);
 
-    // ---- items -------------------------------------------------------------------------
-    for (int item = cta; item < nitems; item += G) {
-      const int t = item / ph.S, ks = item - t * ph.S;
-      const int nchunks = (nseg + kMaxChunkSegs - 1) / kMaxChunkSegs;
-      const int cb = nseg / nchunks, ce = nseg - cb * nchunks;
-      float total[NT][4];
-#pragma unroll
-      for (int j = 0; j < NT; j++) total[j][0] = total[j][1] = total[j][2] = total[j][3] = 0.0f;
-      int segdone = 0;
-      for (int ch = 0; ch < nchunks; ch++) {
-        const int csegs = cb + (ch < ce ? 1 : 0);
-        const int stage = n % plan.stages;
-        const uint32_t par = (n / plan.stages) & 1;
-        const bool ok = mbar_wait(smem_u32(&misc->full[stage]), par, dead);
-        if (ok && warp < csegs) {
-          const int sg = segdone + warp;  // segment index within the slice
-          const uint32_t r_lo = ring + stage * kStageBytes + g * kRowStride + warp * kSegBytes;
-          const uint32_t r_hi = r_lo + 8 * kRowStride;
-          const uint32_t xaddr = smem_u32(xs) + sg * 512 + c * 16;
+    __syncthreads();
+    stamp(1 + 4 * phs);
 
-          if constexpr (QT == MLXR_Q4_K) {
-            const uint4 hl = lds128(r_lo), hh = lds128(r_hi);
-            // 6-bit fields (q_gemm_dequant.metal:222-242) straight from the packed words
-            float ssl[4], ssh[4];
-            uint32_t amin_lo, amin_hi;
-            {
-              const __half2 dl = *reinterpret_cast<const __half2*>(&hl.x), dh = *reinterpret_cast<const __half2*>(&hh.x);
-              const uint32_t w2 = hl.y, w3 = hl.z, v2 = hh.y, v3 = hh.z;
-              const int scl[4] = {(int)(w2 & 63u), (int)((w2 >> 12) & 63u), (int)((w2 >> 24) & 63u), (int)((w3 >> 4) & 63u)};
-              const int sch[4] = {(int)(v2 & 63u), (int)((v2 >> 12) & 63u), (int)((v2 >> 24) & 63u), (int)((v3 >> 4) & 63u)};
+    const TileLane tl = tile_lane(ph, cta, G, group, NG);
+    {
+      // this warp's K part of the slice
+      const int s0w = (wg * nseg) / kGroupWarps, nsw = ((wg + 1) * nseg) / kGroupWarps - s0w;
+      const int nch = (nsw + kStageSegs - 1) / kStageSegs;
+      for (int it = 0; it < tl.count; it++, qg++) {
+        float total[NT][2];
 #pragma unroll
-              for (int p = 0; p < 4; p++) {
-                ssl[p] = __half2float(__hmul(__int2half_rn(scl[p]), __low2half(dl)));
-                ssh[p] = __half2float(__hmul(__int2half_rn(sch[p]), __low2half(dh)));
-              }
-              // this thread supplies the min of pair c (k-slots 2c, 2c+1 of the k8 MMA)
-              const uint32_t mnl = c == 0 ? (w2 >> 6) : c == 1 ? (w2 >> 18) : c == 2 ? ((w2 >> 30) | ((w3 & 15u) << 2)) : (w3 >> 10);
-              const uint32_t mnh = c == 0 ? (v2 >> 6) : c == 1 ? (v2 >> 18) : c == 2 ? ((v2 >> 30) | ((v3 & 15u) << 2)) : (v3 >> 10);
-              const __half sml = __hmul(__int2half_rn((int)(mnl & 63u)), __high2half(dl));
-              const __half smh = __hmul(__int2half_rn((int)(mnh & 63u)), __high2half(dh));
-              amin_lo = (uint32_t)__half_as_ushort(sml) * 0x00010001u;
-              amin_hi = (uint32_t)__half_as_ushort(smh) * 0x00010001u;
-            }
-            constexpr int order[8] = {0, 2, 3, 1, 4, 6, 7, 5};
-            constexpr int pair_of[8] = {0, 0, 0, 1, 2, 2, 2, 3};
-            constexpr bool last_of_pair[8] = {false, false, true, true, false, false, true, true};
-            float acc[NT][4];
-#pragma unroll
-            for (int j = 0; j < NT; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-              const int s = order[i];
-              uint32_t al[4], ah[4];
-              nibbles_to_half2(lds32(r_lo + 16 + 16 * s + 4 * c), al);
-              nibbles_to_half2(lds32(r_hi + 16 + 16 * s + 4 * c), ah);
+        for (int j = 0; j < NT; j++) total[j][0] = total[j][1] = 0.0f;
+        for (int ch = 0; ch < nch; ch++) {
+          const int csegs = min(kStageSegs, nsw - ch * kStageSegs);
+          const uint8_t* st = ring_g + (size_t)(n_consumed % D) * kStageBytes + rg * kRowStride;
+          mbar_wait(smem_u32(&misc->full[warp][n_consumed % D]), (n_consumed / D) & 1, &misc->dead);
+          if (it == 0 && ch == 0 && warp == 0) stamp(2 + 4 * phs);
+          for (int sl = 0; sl < csegs; sl++) {
+            const int sg = s0w + ch * kStageSegs + sl;  // segment index within the slice
+            if constexpr (PAIRS) {
+              segment_mma_pairs<NT>(st + sl * kSegBytes, st + sl * kSegBytes + 8 * kRowStride,
+                                    smem + plan.off_x + (size_t)g * plan.x_stride + sg * 256 + 32 * c, 8 * plan.x_stride,
+                                    reinterpret_cast<const float*>(aux) + sg * 4 + c, plan.aux_stride,
+                                    delta + sg, plan.seg_stride, c, sh1, sh2, total);
+            } else {
+              const uint8_t* xb[NT];
+              const uint32_t* auxp[NT];
+              float dl[NT];
 #pragma unroll
               for (int j = 0; j < NT; j++) {
-                uint4 b = make_uint4(0u, 0u, 0u, 0u);
-                if (g + 8 * j < M) b = lds128(xaddr + (uint32_t)(g + 8 * j) * plan.x_stride + 64 * s);
-                mma16816(acc[j], al[0], ah[0], al[1], ah[1], b.x, b.y);
-                mma16816(acc[j], al[2], ah[2], al[3], ah[3], b.z, b.w);
+                const int b = (g >> 1) + 4 * j;    // MMA column g = (batch b, part g & 1)
+                xb[j] = b < M ? smem + plan.off_x + (size_t)(2 * b + (g & 1)) * plan.x_stride + sg * 256 + c * 8 : nullptr;
+                auxp[j] = (b < M && !(g & 1)) ? aux + (size_t)b * plan.aux_stride + sg * AUXW : nullptr;
+                dl[j] = (c + 4 * j) < M ? delta[(c + 4 * j) * plan.seg_stride + sg] : 0.0f;
               }
-              if (last_of_pair[i]) {
-                const int p = pair_of[i];
-#pragma unroll
-                for (int j = 0; j < NT; j++) {
-                  total[j][0] = fmaf(ssl[p], acc[j][0], total[j][0]);
-                  total[j][1] = fmaf(ssl[p], acc[j][1], total[j][1]);
-                  total[j][2] = fmaf(ssh[p], acc[j][2], total[j][2]);
-                  total[j][3] = fmaf(ssh[p], acc[j][3], total[j][3]);
-                  acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
-                }
-              }
-            }
-            // min term: sum_p sm_p * Sx_p, Sx_p as hi + lo halves
-#pragma unroll
-            for (int j = 0; j < NT; j++) {
-              uint32_t b = 0u;
-              if (g + 8 * j < M) b = sxp[(size_t)(g + 8 * j) * plan.sxp_stride + sg * 4 + c];
-              mma1688(total[j], amin_lo, amin_hi, b);
-            }
-          } else {  // Q4_0: 8 blocks of 18 B; scale at +18s, nibbles at +18s+2
-#pragma unroll
-            for (int s = 0; s < 8; s++) {
-              uint32_t wl, wh;
-              if (s & 1) {  // 18s+2 is 4-byte aligned
-                wl = lds32(r_lo + 18 * s + 2 + 4 * c);
-                wh = lds32(r_hi + 18 * s + 2 + 4 * c);
-              } else {      // straddles two words
-                wl = __funnelshift_r(lds32(r_lo + 18 * s + 4 * c), lds32(r_lo + 18 * s + 4 * c + 4), 16);
-                wh = __funnelshift_r(lds32(r_hi + 18 * s + 4 * c), lds32(r_hi + 18 * s + 4 * c + 4), 16);
-              }
-              uint32_t sl, sh;
-              asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sl) : "r"(r_lo + 18 * s));
-              asm volatile("ld.shared.u16 %0, [%1];" : "=r"(sh) : "r"(r_hi + 18 * s));
-              const float fl = __half2float(__ushort_as_half((unsigned short)sl));
-              const float fh = __half2float(__ushort_as_half((unsigned short)sh));
-              uint32_t al[4], ah[4];
-              nibbles_to_half2(wl, al);
-              nibbles_to_half2(wh, ah);
-#pragma unroll
-              for (int j = 0; j < NT; j++) {
-                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                uint4 b = make_uint4(0u, 0u, 0u, 0u);
-                if (g + 8 * j < M) b = lds128(xaddr + (uint32_t)(g + 8 * j) * plan.x_stride + 64 * s);
-                mma16816(acc, al[0], ah[0], al[1], ah[1], b.x, b.y);
-                mma16816(acc, al[2], ah[2], al[3], ah[3], b.z, b.w);
-                total[j][0] = fmaf(fl, acc[0], total[j][0]);
-                total[j][1] = fmaf(fl, acc[1], total[j][1]);
-                total[j][2] = fmaf(fh, acc[2], total[j][2]);
-                total[j][3] = fmaf(fh, acc[3], total[j][3]);
-              }
+              segment_mma<QT, NT>(st + sl * kSegBytes, st + sl * kSegBytes + 8 * kRowStride, xb, auxp, dl, lane, total);
             }
           }
+          n_consumed++;
+          __syncwarp();
+          issue();   // refill the stage that was just drained
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&misc->empty[stage]));
-        segdone += csegs;
-        n++;
-      }
-
-      // ---- reduce the eight warps' partial sums: tilebuf[row][col] in true units ---------
+        if (it == 0 && warp == 0) stamp(3 + 4 * phs);
+        // hand the partial sums to the epilogue warp through the tile's slot
+        const int slot = qg % kSlots;
+        if (qg >= kSlots) bar_sync(bar_free0 + slot, kFreeThreads);   // slot read out by its last duty warp
+        float* mine = slots + ((size_t)slot * kGroupWarps + wg) * kTileRows * MB;
+        if constexpr (PAIRS) {
+          // the four lanes of a quad hold the four pairs' parts of (row, batch): add them here so
+          // that the epilogue warp has 16 x NT values per warp to read instead of 16 x 4 NT
 #pragma unroll
-      for (int j = 0; j < NT; j++) {
-        float* rw = red + (size_t)warp * kTileRows * MC;
-        *reinterpret_cast<float2*>(&rw[g * MC + 8 * j + 2 * c]) = make_float2(total[j][0], total[j][1]);
-        *reinterpret_cast<float2*>(&rw[(g + 8) * MC + 8 * j + 2 * c]) = make_float2(total[j][2], total[j][3]);
-      }
-      consumer_sync();
-      for (int e = ctid; e < kTileRows * MC; e += kConsumerWarps * 32) {
-        float v = 0.0f;
+          for (int j = 0; j < NT; j++) {
 #pragma unroll
-        for (int w8 = 0; w8 < kConsumerWarps; w8++) v += red[(size_t)w8 * kTileRows * MC + e];
-        tilebuf[e] = v * misc->colscale[e % MC];
-      }
-      consumer_sync();
-
-      // ---- split-K: park the partial, the last slice to arrive reduces all of them -------
-      bool do_epilogue = true;
-      if (ph.S > 1) {
-        const size_t slab = (size_t)ph.ntiles * kTileRows * MC;
-        float* mine = ph.partials + (size_t)ks * slab + (size_t)t * kTileRows * MC;
-        for (int e = ctid; e < kTileRows * MC; e += kConsumerWarps * 32) __stcg(&mine[e], tilebuf[e]);
-        __threadfence();
-        consumer_sync();
-        if (ctid == 0) {
-          const uint32_t prev = atomicAdd(&ph.counters[t], 1u);
-          misc->last_flag = (prev == (uint32_t)ph.S - 1u);
-          if (misc->last_flag) ph.counters[t] = 0u;   // self-cleaning for the next launch
-          __threadfence();
-        }
-        consumer_sync();
-        do_epilogue = misc->last_flag != 0;
-        if (do_epilogue) {
-          for (int e = ctid; e < kTileRows * MC; e += kConsumerWarps * 32) {
-            float v = 0.0f;
-            for (int s2 = 0; s2 < ph.S; s2++) v += __ldcg(&ph.partials[(size_t)s2 * slab + (size_t)t * kTileRows * MC + e]);
-            tilebuf[e] = v;
-          }
-          consumer_sync();
-        }
-      }
-
-      // ---- epilogue ----------------------------------------------------------------------
-      if (do_epilogue) {
-        if (ph.interleave) {
-          // rows 0..7 gate, 8..15 up of the same 8 intermediate indices: h = SiLU(g) * u
-          for (int e = ctid; e < 8 * MC; e += kConsumerWarps * 32) {
-            const int r = e / MC, m = e % MC;
-            const int col = 8 * t + r;
-            if (m < M && col < ph.n_total) {
-              const float gv = Act<T>::to_f(Act<T>::from_f(tilebuf[r * MC + m]));
-              const float uv = Act<T>::to_f(Act<T>::from_f(tilebuf[(r + 8) * MC + m]));
-              reinterpret_cast<T*>(ph.y[0])[(size_t)m * ph.n_total + col] = Act<T>::from_f(swish_f(gv) * uv);
+            for (int h = 0; h < 2; h++) {
+              float v = total[j][h];
+              v += __shfl_xor_sync(0xffffffffu, v, 1);
+              v += __shfl_xor_sync(0xffffffffu, v, 2);
+              if (c == 0) mine[(rg + 8 * h) * NT + j] = v;
             }
           }
         } else {
-          // pairs of adjacent rows (2j, 2j+1): plain store or RoPE rotation
-          for (int e = ctid; e < 8 * MC; e += kConsumerWarps * 32) {
-            const int j = e / MC, m = e % MC;
-            int R = kTileRows * t + 2 * j;
-            if (m >= M || R >= ph.n_total) continue;
-            int mat = 0;
-            if (ph.nmat > 1 && R >= ph.rows[0]) { R -= ph.rows[0]; mat = 1; if (ph.nmat > 2 && R >= ph.rows[1]) { R -= ph.rows[1]; mat = 2; } }
-            const bool has_odd = R + 1 < ph.rows[mat];
-            float ve = tilebuf[(2 * j) * MC + m], vo = tilebuf[(2 * j + 1) * MC + m];
-            const T* bias = reinterpret_cast<const T*>(ph.bias[mat]);
-            if (bias) { ve += Act<T>::to_f(bias[R]); if (has_odd) vo += Act<T>::to_f(bias[R + 1]); }
-            T* out = reinterpret_cast<T*>(ph.y[mat]) + (size_t)m * ph.rows[mat] + R;
-            if (ph.epi[mat] == kEpiRope) {
-              const float qe = Act<T>::to_f(Act<T>::from_f(ve)), qo = Act<T>::to_f(Act<T>::from_f(vo));
-              const long long pos = (long long)ph.positions[m] + ph.pos_offset;
-              if (pos < 0 || pos >= ph.max_seq) { atomicExch(P.status, MLXR_ERR_SHAPE); continue; }
-              const int pairs = ph.head_dim >> 1, pi = (R % ph.head_dim) >> 1;
-              const float cs = __half2float(ph.cos_t[(size_t)pos * pairs + pi]);
-              const float sn = __half2float(ph.sin_t[(size_t)pos * pairs + pi]);
-              out[0] = Act<T>::from_f(__fsub_rn(__fmul_rn(qe, cs), __fmul_rn(qo, sn)));
-              out[1] = Act<T>::from_f(__fadd_rn(__fmul_rn(qo, cs), __fmul_rn(qe, sn)));
-            } else {
-              out[0] = Act<T>::from_f(ve);
-              if (has_odd) out[1] = Act<T>::from_f(vo);
-            }
+#pragma unroll
+          for (int j = 0; j < NT; j++) {
+            mine[rg * MB + 4 * j + c] = total[j][0];
+            mine[(rg + 8) * MB + 4 * j + c] = total[j][1];
           }
         }
+        if (wg != (qg & (kGroupWarps - 1))) {
+          bar_arrive(bar_full0 + slot, kFullThreads);
+        } else {
+          // ===== this warp is on duty for the tile =====
+          const int t = tl.first + it * tl.step;
+          float* tile = tiles + (size_t)slot * kTileRows * MB;
+          bar_sync(bar_full0 + slot, kFullThreads);   // all eight partials are in the slot
+          const float* sl0 = slots + (size_t)slot * kGroupWarps * kTileRows * MB;
+          if constexpr (PAIRS) {
+            // slot rows are [16][NT]; the tile buffer stays [16][MB] for the common epilogue
+            for (int e = lane; e < kTileRows * NT; e += 32) {
+              float v = 0.0f;
+#pragma unroll
+              for (int w8 = 0; w8 < kGroupWarps; w8++) v += sl0[w8 * kTileRows * MB + e];
+              tile[(e / NT) * MB + (e % NT)] = v;
+            }
+          } else {
+            for (int e = lane; e < kTileRows * MB; e += 32) {
+              float v = 0.0f;
+#pragma unroll
+              for (int w8 = 0; w8 < kGroupWarps; w8++) v += sl0[w8 * kTileRows * MB + e];
+              tile[e] = v;
+            }
+          }
+          __syncwarp();
+          if (qg + kSlots < total_q) bar_arrive(bar_free0 + slot, kFreeThreads);  // hand the slot back
+          tile_epilogue<T, MB>(P, ph, tile, t, ks, lane);
+          __syncwarp();
+        }
       }
-      consumer_sync();  // tilebuf / red are reused by the next item
     }
   }
-  if (ctid == 0 && *dead) atomicExch(P.status, MLXR_ERR_TIMEOUT);
+  stamp(15);
+  __syncthreads();
+  if (tid == 0 && misc->dead) atomicExch(P.status, MLXR_ERR_TIMEOUT);
 }
 
 }  // namespace decode

@@ -13,6 +13,8 @@ int launch_dequantize(const void* w, void* out, int N, int K, int qt, int out_dt
                       cudaStream_t st);
 int launch_qgemm_generic(const void* x, const void* w, const void* bias, void* y, int M, int N,
                          int K, int qt, int dtype, cudaStream_t st);
+int launch_linear_dense(const void* x, const void* w, const void* bias, void* y, int M, int N, int K,
+                        int dtype, cudaStream_t st);
 int launch_rmsnorm(const void* x, const void* w, const void* res, void* y, int rows, int hidden,
                    float eps, int dtype, cudaStream_t st);
 int launch_swiglu(const void* g, const void* u, void* o, size_t n, int dtype, cudaStream_t st);
@@ -41,6 +43,7 @@ struct DecodeLinear {
   int head_dim, max_seq, pos_offset;
 };
 constexpr size_t kDecodeScratchBytes = (size_t)8 << 20;  // split-K partial sums
+void set_decode_trace(void* dev_ptr);
 bool decode_supported(int qt, int M, int K, const void* const* w, int nmat);
 int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype, void* scratch,
                   size_t scratch_bytes, uint32_t* sync, uint32_t* bar_host, int* status, cudaStream_t st);

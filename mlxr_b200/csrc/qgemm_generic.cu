@@ -50,6 +50,52 @@ __global__ void __launch_bounds__(128) qgemm_generic_kernel(
   }
 }
 
+// Dense weights W[N,K] of the activation dtype (the unquantized Linear / swiglu_mlp of the
+// reference): same one-warp-per-row scheme, fp32 accumulation.
+template <typename T, int MT>
+__global__ void __launch_bounds__(128) linear_dense_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                                                           const T* __restrict__ bias, T* __restrict__ y,
+                                                           int M, int N, int K) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 4 + warp;
+  if (n >= N) return;
+  const T* row = w + (size_t)n * K;
+  for (int m0 = blockIdx.y * MT; m0 < M; m0 += gridDim.y * MT) {
+    float acc[MT];
+#pragma unroll
+    for (int i = 0; i < MT; i++) acc[i] = 0.0f;
+    for (int k = lane; k < K; k += 32) {
+      const float wv = Act<T>::to_f(row[k]);
+#pragma unroll
+      for (int i = 0; i < MT; i++)
+        if (m0 + i < M) acc[i] = fmaf(Act<T>::to_f(x[(size_t)(m0 + i) * K + k]), wv, acc[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < MT; i++) {
+      const float r = warp_sum(acc[i]);
+      if (lane == 0 && m0 + i < M) {
+        float v = r;
+        if (bias) v += Act<T>::to_f(bias[n]);
+        y[(size_t)(m0 + i) * N + n] = Act<T>::from_f(v);
+      }
+    }
+  }
+}
+
+int launch_linear_dense(const void* x, const void* w, const void* bias, void* y, int M, int N, int K,
+                        int dtype, cudaStream_t st) {
+  if (M == 0 || N == 0) return MLXR_OK;
+  constexpr int MT = 4;
+  int gy = (M + MT - 1) / MT;
+  if (gy > 4096) gy = 4096;
+  dim3 grid((N + 3) / 4, gy);
+  MLXR_DISPATCH_DTYPE(dtype, T, {
+    linear_dense_kernel<T, MT><<<grid, 128, 0, st>>>((const T*)x, (const T*)w, (const T*)bias, (T*)y, M, N, K);
+  });
+  MLXR_LAUNCH_CHECK("linear_dense_kernel");
+  return MLXR_OK;
+}
+
 int launch_qgemm_generic(const void* x, const void* w, const void* bias, void* y, int M, int N,
                          int K, int qt, int dtype, cudaStream_t st) {
   if (M == 0 || N == 0) return MLXR_OK;
