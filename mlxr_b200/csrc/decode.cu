@@ -78,7 +78,7 @@ bool decode_supported(int qt, int M, int K, const void* const* w, int nmat) {
 static int choose_slices(int ntiles, int nseg, int G, int ng, int M, int xrows, int max_x_bytes, bool fixed_grid) {
   double best = 1e30;
   int bestS = 0;
-  for (int S = 1; S <= std::min(nseg, 16); S++) {
+  for (int S = 1; S <= std::min(nseg, 16); S *= 2) {   // powers of two: slice and lane by shift and mask
     if (fixed_grid && (G % S != 0)) continue;
     const int g = fixed_grid ? G : (G / S) * S;
     if (g < 1) continue;
@@ -176,7 +176,7 @@ int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype
     ph.row_bytes = nseg * kSegBytes;
     ph.ntiles = L.interleave ? (ph.n_total + 7) / 8 : (ph.n_total + kTileRows - 1) / kTileRows;
     int S = choose_slices(ph.ntiles, nseg, G, NG, M, xrows, max_x, nphases > 1 || i > 0);
-    if (const char* e = getenv("MLXR_DEC_S")) { const int v = atoi(e); if (v >= 1 && v <= nseg && (nphases == 1 || G % v == 0)) S = v; }  // tuning override
+    if (const char* e = getenv("MLXR_DEC_S")) { const int v = atoi(e); if (v >= 1 && v <= nseg && (v & (v - 1)) == 0 && (nphases == 1 || G % v == 0)) S = v; }  // tuning override
     if (S <= 0) {
       if (NG == 2 && !getenv("MLXR_DEC_GROUPS")) {   // not enough shared memory beside 16 rings: one group
         setenv("MLXR_DEC_GROUPS", "1", 1);
@@ -189,6 +189,8 @@ int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype
     }
     if (nphases == 1) G = (G / S) * S;
     ph.S = S;
+    ph.s_shift = 0;
+    while ((1 << ph.s_shift) < S) ph.s_shift++;
     ph.segs_base = nseg / S;
     ph.segs_extra = nseg % S;
     ph.max_slice_segs = ph.segs_base + (ph.segs_extra ? 1 : 0);
@@ -211,6 +213,12 @@ int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype
       ph.counters = sync + counter_off;
       counter_off += ph.ntiles;
     }
+  }
+  for (int i = 0; i < nphases; i++) {
+    Phase& ph = P.ph[i];
+    ph.lane_step = (G / ph.S) * NG;
+    ph.lane_q = (ph.ntiles - 1) / ph.lane_step;
+    ph.lane_r = (ph.ntiles - 1) % ph.lane_step;
   }
   // shared-memory plan: as many ring stages per warp as fit
   int stages = kMaxStages;

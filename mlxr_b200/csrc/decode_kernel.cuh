@@ -4,10 +4,9 @@
 // itself with 2-D tensor TMA copies (cp.async.bulk.tensor.2d, one box of 8 rows x 288 bytes
 // per half tile, completion on an mbarrier) and drains itself, so nothing inside the stream
 // waits on another warp and the copy costs one instruction per stage.  A 16-row weight tile's K range is split over the eight warps of a group;
-// each leaves its partial sums in a shared-memory slot and signals a hardware named barrier;
-// the warp on duty for that tile (tile number modulo 8, so the duty rotates) waits on the
-// barrier, adds the eight partials in warp order (deterministic) and runs the epilogue and
-// the split-K fix-up.
+// each leaves its partial sums in a shared-memory slot and bumps the slot's counter; the warp
+// that arrives last adds the eight partials in warp order (deterministic) and runs the
+// epilogue and the split-K fix-up, so nobody waits for anybody.
 // (Measured and dropped: one-dimensional cp.async.bulk copies of a few hundred bytes -- an SM
 // keeps only a handful in flight, 0.5 TB/s in total; 16-byte cp.async -- the LSU needs ~14
 // cycles per 18-lane instruction, which caps the stream at 4.4 TB/s and delays every other
@@ -31,7 +30,7 @@
 //   two phases gate/up -> grid barrier -> down in ONE launch: every warp keeps its ring
 //              full with the next phase's weights while the CTA waits at the barrier
 // The only spin wait (grid barrier) is bounded; on expiry a status word is set and the
-// kernel carries on without blocking.  Named barriers involve only warps of the CTA.
+// kernel carries on without blocking.
 #pragma once
 #include <cuda.h>   // CUtensorMap (type only; the encoder is fetched at run time)
 
@@ -62,7 +61,10 @@ struct Phase {
   int K;
   int row_bytes;
   int ntiles;
-  int S;                 // K-slices handled by different CTAs (gridDim.x % S == 0)
+  int S;                 // K-slices handled by different CTAs: a power of two dividing gridDim.x
+  int s_shift;           // log2(S)
+  int lane_step;         // (gridDim.x / S) * groups: (CTA, group) pairs sharing the tiles of a slice
+  int lane_q, lane_r;    // ntiles - 1 = lane_q * lane_step + lane_r (host-side division)
   int segs_base, segs_extra;  // slice s has segs_base + (s < segs_extra) segments
   int max_slice_segs;
   // activations
@@ -89,8 +91,8 @@ struct Params {
   Phase ph[2];
   int nphases;
   int M;
-  uint32_t* gridbar;     // monotonically increasing arrival counter
-  uint32_t bar_base;     // value of *gridbar before this launch
+  uint32_t* gridbar;     // two words: arrival count, generation (self-resetting grid barrier)
+  uint32_t bar_base;     // unused
   int* status;
   unsigned long long* trace;  // optional: 16 globaltimer stamps per CTA (null = off)
 };
@@ -101,7 +103,7 @@ struct SmemPlan {
   int x_stride;      // bytes per (batch, part) row of the int8 x slice
   int aux_stride;    // words per batch column of the sum table
   int seg_stride;    // floats per batch column of the delta table
-  int off_ring, off_x, off_aux, off_delta, off_slots, off_tile, off_misc, total;
+  int off_ring, off_x, off_aux, off_delta, off_slots, off_tile, off_params, off_misc, total;
 };
 // aux words per segment: Q4_K 4 (pair sums hi|lo), Q4_0 8 (4 hi words + 4 lo words)
 // pairs: the batch <= 2 mapping (8 masked x rows per batch); else 2 rows (hi, lo) per batch
@@ -117,9 +119,8 @@ __host__ __device__ inline SmemPlan make_plan(int ng, int stages, int max_slice_
   p.off_delta = p.off_aux + M * p.aux_stride * 4;
   p.off_slots = (p.off_delta + M * p.seg_stride * 4 + 15) & ~15;
   p.off_tile = p.off_slots + ng * kSlots * kGroupWarps * kTileRows * MB * 4;
-  p.off_misc = p.off_tile + ng * kSlots * kTileRows * MB * 4;
-  p.off_misc = (p.off_misc + 15) & ~15;
-  p.off_misc = (p.off_misc + 127) & ~127;
+  p.off_params = (p.off_tile + ng * kSlots * kTileRows * MB * 4 + 127) & ~127;
+  p.off_misc = (p.off_params + (int)sizeof(Params) + 127) & ~127;
   p.total = p.off_misc + 1024;
   return p;
 }
@@ -127,6 +128,8 @@ __host__ __device__ inline SmemPlan make_plan(int ng, int stages, int max_slice_
 struct Misc {
   unsigned long long full[2 * kGroupWarps][kMaxStages];   // one mbarrier per compute warp and stage
   float redbuf[32];
+  int slot_free[2][kSlots];   // highest tile number that may write into the slot
+  int slot_cnt[2][kSlots];    // warps that have delivered their partial sums for the slot's tile
   int dead;
 };
 static_assert(sizeof(Misc) <= 1024, "Misc must fit its smem slot");
@@ -208,9 +211,10 @@ __device__ __forceinline__ const uint8_t* tile_row(const Phase& ph, int t, int r
 struct TileLane { int first, step, count; };
 __device__ __forceinline__ TileLane tile_lane(const Phase& ph, int cta, int G, int group, int ng) {
   TileLane tl;
-  tl.step = (G / ph.S) * ng;
-  tl.first = (cta / ph.S) * ng + group;
-  tl.count = tl.first < ph.ntiles ? (ph.ntiles - 1 - tl.first) / tl.step + 1 : 0;
+  tl.step = ph.lane_step;
+  tl.first = (cta >> ph.s_shift) * ng + group;
+  // floor((ntiles - 1 - first) / step) + 1 without a division (first < step)
+  tl.count = tl.first <= ph.lane_r ? ph.lane_q + 1 : ph.lane_q;
   return tl;
 }
 
@@ -668,14 +672,22 @@ __device__ __forceinline__ void tile_epilogue(const Params& P, const Phase& ph, 
 // in the MMA columns, four batch rows per n-tile.
 template <int QT, typename T, int NT, int NG, bool PAIRS>
 __global__ void __launch_bounds__(NG * kGroupWarps * 32, 1)
-decode_kernel(const __grid_constant__ Params P, const __grid_constant__ SmemPlan plan) {
+decode_kernel(const __grid_constant__ Params Pg, const __grid_constant__ SmemPlan plan) {
   extern __shared__ __align__(128) uint8_t smem[];
+  // The parameter block is copied to shared memory by all threads at once: read piecemeal from
+  // the constant bank, its ~20 cache lines miss one after another (measured: 2.8 us of set-up).
+  // Only the tensor maps are used in place (the TMA unit reads them through their address).
+  {
+    uint32_t* dst = reinterpret_cast<uint32_t*>(smem + plan.off_params);
+    const uint32_t* src = reinterpret_cast<const uint32_t*>(&Pg);
+    for (int i = threadIdx.x; i < (int)(sizeof(Params) / 4); i += blockDim.x) dst[i] = src[i];
+  }
+  __syncthreads();
+  const Params& P = *reinterpret_cast<const Params*>(smem + plan.off_params);
   constexpr int MB = 4 * NT;                       // batch columns held (two MMA columns each)
   constexpr int AUXW = (QT == MLXR_Q4_K) ? 4 : 8;
   constexpr int kComputeWarps = NG * kGroupWarps;
   constexpr int kAllWarps = kComputeWarps;
-  constexpr int kFullThreads = kGroupWarps * 32;        // seven arrive + the duty warp syncs
-  constexpr int kFreeThreads = (kGroupWarps + 1) * 32;  // eight writers sync + the duty warp's earlier arrive
   Misc* misc = reinterpret_cast<Misc*>(smem + plan.off_misc);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
@@ -688,10 +700,11 @@ decode_kernel(const __grid_constant__ Params P, const __grid_constant__ SmemPlan
   const int D = plan.stages;
   const int group = warp / kGroupWarps;
   const int wg = warp % kGroupWarps;               // compute warp's index in its group
-  const int bar_full0 = 1 + group * 2 * kSlots, bar_free0 = bar_full0 + kSlots;
 
   if (tid == 0) {
     misc->dead = 0;
+    for (int gi = 0; gi < 2; gi++)
+      for (int sl = 0; sl < kSlots; sl++) { misc->slot_free[gi][sl] = kSlots - 1; misc->slot_cnt[gi][sl] = 0; }
     for (int w = 0; w < kComputeWarps; w++)
       for (int st = 0; st < D; st++) mbar_init(smem_u32(&misc->full[w][st]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -724,7 +737,7 @@ decode_kernel(const __grid_constant__ Params P, const __grid_constant__ SmemPlan
   auto enter_phase = [&]() {   // first phase >= i_phs with work for this warp
     while (i_phs < P.nphases) {
       const Phase& ph = P.ph[i_phs];
-      const int ks = cta % ph.S, nseg = slice_segs(ph, ks);
+      const int ks = (cta & (ph.S - 1)), nseg = slice_segs(ph, ks);
       const int s0 = (wg * nseg) / kGroupWarps, s1 = ((wg + 1) * nseg) / kGroupWarps;
       i_nsw = s1 - s0;
       i_seg_first = slice_seg0(ph, ks) + s0;
@@ -736,7 +749,8 @@ decode_kernel(const __grid_constant__ Params P, const __grid_constant__ SmemPlan
       i_phs++;
     }
   };
-  uint32_t n_issued = 0, n_consumed = 0;
+  int st_issue = 0, st_cons = 0;      // ring positions (no runtime division in the stream)
+  uint32_t par_cons = 0;
   // One stage = two TMA boxes (rows 0-7 and 8-15 of the tile, 288 bytes wide) signalling the
   // stage's mbarrier; issued by lane 0.  Rows past the end of a matrix and bytes past the end
   // of a row are zero-filled by the TMA unit (and still counted in the transaction bytes).
@@ -745,9 +759,8 @@ decode_kernel(const __grid_constant__ Params P, const __grid_constant__ SmemPlan
     const Phase& ph = P.ph[i_phs];
     if (lane == 0) {
       const int t = i_tl.first + i_tile * i_tl.step;
-      const int stage = n_issued % D;
-      const uint32_t bar = smem_u32(&misc->full[warp][stage]);
-      const uint32_t dst = ring + stage * kStageBytes;
+      const uint32_t bar = smem_u32(&misc->full[warp][st_issue]);
+      const uint32_t dst = ring + st_issue * kStageBytes;
       const int x = (i_seg_first + i_ch * kStageSegs) * (kSegBytes / 8);
       int m0 = 0, y0, m1, y1;
       if (ph.interleave) { y0 = 8 * t; m1 = 1; y1 = 8 * t; }
@@ -760,10 +773,10 @@ decode_kernel(const __grid_constant__ Params P, const __grid_constant__ SmemPlan
         }
       }
       mbar_arrive_expect_tx(bar, kStageBytes);
-      tma_load_2d(dst, &P.tmap[i_phs][m0], x, y0, bar);
-      tma_load_2d(dst + 8 * kRowStride, &P.tmap[i_phs][m1], x, y1, bar);
+      tma_load_2d(dst, &Pg.tmap[i_phs][m0], x, y0, bar);
+      tma_load_2d(dst + 8 * kRowStride, &Pg.tmap[i_phs][m1], x, y1, bar);
     }
-    n_issued++;
+    if (++st_issue == D) st_issue = 0;
     if (++i_ch >= i_nch) {
       i_ch = 0;
       if (++i_tile >= i_tl.count) { i_phs++; enter_phase(); }
@@ -775,7 +788,7 @@ decode_kernel(const __grid_constant__ Params P, const __grid_constant__ SmemPlan
   bool have_pre = false;
   {
     const Phase& ph0 = P.ph[0];
-    const int ks0 = cta % ph0.S, nseg0 = slice_segs(ph0, ks0);
+    const int ks0 = (cta & (ph0.S - 1)), nseg0 = slice_segs(ph0, ks0);
     if (warp < nseg0 && tile_lane(ph0, cta, G, 0, NG).count > 0) {
       const size_t k = (size_t)(slice_seg0(ph0, ks0) + warp) * 256 + lane * 8;
       load8(reinterpret_cast<const T*>(ph0.x) + k, pre);
@@ -793,26 +806,36 @@ decode_kernel(const __grid_constant__ Params P, const __grid_constant__ SmemPlan
     const Phase& ph = P.ph[phs];
     if (phs > 0) {
       // ---- grid barrier: every CTA has finished (and made visible) the previous phase ----
-      __threadfence();
+      if (warp == 0) stamp(8);
       __syncthreads();
+      stamp(9);
       if (tid == 0) {
-        const uint32_t target = P.bar_base + (uint32_t)phs * (uint32_t)G;
-        atomicAdd(P.gridbar, 1u);
-        bool ok = false;
-        for (uint32_t i = 0; i < kSpinLimit; i++) {
-          const uint32_t v = *reinterpret_cast<volatile uint32_t*>(P.gridbar);
-          if ((int32_t)(v - target) >= 0) { ok = true; break; }
-          __nanosleep(20);
-        }
-        if (!ok) misc->dead = 1;
+        // self-resetting barrier (safe under CUDA-graph replay): word 0 counts arrivals, word 1 is
+        // the generation; the last CTA to arrive clears the count and bumps the generation.
+        // The CTA barrier above orders every thread's stores before this thread's fence.
+        uint32_t gen;
+        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(gen) : "l"(P.gridbar + 1) : "memory");
         __threadfence();
+        if (atomicAdd(P.gridbar, 1u) == (uint32_t)G - 1u) {
+          atomicExch(P.gridbar, 0u);          // nobody touches the count again before the next launch
+          asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(P.gridbar + 1) : "memory");
+        } else {
+          bool ok = false;
+          for (uint32_t i = 0; i < kSpinLimit; i++) {
+            uint32_t now;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(now) : "l"(P.gridbar + 1) : "memory");
+            if (now != gen) { ok = true; break; }
+          }
+          if (!ok) misc->dead = 1;
+        }
       }
       __syncthreads();
+      stamp(10);
     }
     // group 0 owns the lowest tile of the CTA: no tile there means no work in this phase
     if (tile_lane(ph, cta, G, 0, NG).count == 0) continue;   // uniform per CTA
 
-    const int ks = cta % ph.S;
+    const int ks = (cta & (ph.S - 1));
     const int nseg = slice_segs(ph, ks), seg0 = slice_seg0(ph, ks);
     x_prologue<QT, T, PAIRS>(ph, plan, smem, misc, M, nseg, seg0, kAllWarps, have_pre && phs == 0, pre, gpre,
                              (P.trace && phs == 0) ? P.trace + (size_t)cta * 16 : nullptr);
@@ -831,8 +854,8 @@ decode_kernel(const __grid_constant__ Params P, const __grid_constant__ SmemPlan
         for (int j = 0; j < NT; j++) total[j][0] = total[j][1] = 0.0f;
         for (int ch = 0; ch < nch; ch++) {
           const int csegs = min(kStageSegs, nsw - ch * kStageSegs);
-          const uint8_t* st = ring_g + (size_t)(n_consumed % D) * kStageBytes + rg * kRowStride;
-          mbar_wait(smem_u32(&misc->full[warp][n_consumed % D]), (n_consumed / D) & 1, &misc->dead);
+          const uint8_t* st = ring_g + (size_t)st_cons * kStageBytes + rg * kRowStride;
+          mbar_wait(smem_u32(&misc->full[warp][st_cons]), par_cons, &misc->dead);
           if (it == 0 && ch == 0 && warp == 0) stamp(2 + 4 * phs);
           for (int sl = 0; sl < csegs; sl++) {
             const int sg = s0w + ch * kStageSegs + sl;  // segment index within the slice
@@ -855,14 +878,21 @@ decode_kernel(const __grid_constant__ Params P, const __grid_constant__ SmemPlan
               segment_mma<QT, NT>(st + sl * kSegBytes, st + sl * kSegBytes + 8 * kRowStride, xb, auxp, dl, lane, total);
             }
           }
-          n_consumed++;
+          if (++st_cons == D) { st_cons = 0; par_cons ^= 1u; }
           __syncwarp();
           issue();   // refill the stage that was just drained
         }
         if (it == 0 && warp == 0) stamp(3 + 4 * phs);
         // hand the partial sums to the epilogue warp through the tile's slot
         const int slot = qg % kSlots;
-        if (qg >= kSlots) bar_sync(bar_free0 + slot, kFreeThreads);   // slot read out by its last duty warp
+        // the slot must have been read out by the duty warp of tile qg - kSlots: a flag, not a
+        // barrier, so that the eight writers do not have to meet (bounded poll)
+        {
+          volatile int* fr = &misc->slot_free[group][slot];
+          bool ok = false;
+          for (uint32_t i = 0; i < kSpinLimit; i++) if (*fr >= qg) { ok = true; break; }
+          if (!ok) misc->dead = 1;
+        }
         float* mine = slots + ((size_t)slot * kGroupWarps + wg) * kTileRows * MB;
         if constexpr (PAIRS) {
           // the four lanes of a quad hold the four pairs' parts of (row, batch): add them here so
@@ -884,13 +914,18 @@ decode_kernel(const __grid_constant__ Params P, const __grid_constant__ SmemPlan
             mine[(rg + 8) * MB + 4 * j + c] = total[j][1];
           }
         }
-        if (wg != (qg & (kGroupWarps - 1))) {
-          bar_arrive(bar_full0 + slot, kFullThreads);
-        } else {
-          // ===== this warp is on duty for the tile =====
+        // the warp that delivers last finishes the tile: nobody waits.  Shared-memory stores of
+        // a warp are ordered before its later shared-memory atomic (fence for the memory model)
+        __threadfence_block();
+        __syncwarp();
+        int last = 0;
+        if (lane == 0) last = (atomicAdd(&misc->slot_cnt[group][slot], 1) == kGroupWarps - 1);
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+          // ===== this warp finishes the tile =====
+          __threadfence_block();
           const int t = tl.first + it * tl.step;
           float* tile = tiles + (size_t)slot * kTileRows * MB;
-          bar_sync(bar_full0 + slot, kFullThreads);   // all eight partials are in the slot
           const float* sl0 = slots + (size_t)slot * kGroupWarps * kTileRows * MB;
           if constexpr (PAIRS) {
             // slot rows are [16][NT]; the tile buffer stays [16][MB] for the common epilogue
@@ -909,7 +944,11 @@ decode_kernel(const __grid_constant__ Params P, const __grid_constant__ SmemPlan
             }
           }
           __syncwarp();
-          if (qg + kSlots < total_q) bar_arrive(bar_free0 + slot, kFreeThreads);  // hand the slot back
+          if (lane == 0) {   // hand the slot back
+            misc->slot_cnt[group][slot] = 0;
+            __threadfence_block();
+            *reinterpret_cast<volatile int*>(&misc->slot_free[group][slot]) = qg + kSlots;
+          }
           tile_epilogue<T, MB>(P, ph, tile, t, ks, lane);
           __syncwarp();
         }

@@ -85,7 +85,7 @@ def test_empty_and_single_block(oracle):
     packed = fuzz_blocks(3, 1, 5)
     _, h_ref = oracle.dequantize(packed, 1, 256, 3)
     h = _dequant_gpu(packed, 1, 256, 3, torch.float16).view(torch.int16).numpy().view(np.uint16)
-    assert np.array_equal(h, h_ref)
+    assert_same_half_bits(h, h_ref)
 
 
 def test_full_size_checksum(oracle):
