@@ -192,6 +192,19 @@ MLXR_API int mlxr_mlp_block_dense(const void* x, const void* w_gate, const void*
  * call).  The return value is the status of this call itself. */
 MLXR_API int mlxr_stream_status(void* stream, int* status_out);
 
+/* How the persistent decode kernel is launched (process-wide; no counterpart in the
+ * reference, whose Metal command buffers serialise kernels).
+ *   MLXR_DECODE_LAUNCH_OVERLAPPED (default): plain launch with programmatic stream
+ *     serialization.  The kernel starts its weight copies while the previous kernel of the
+ *     stream drains and waits (griddepcontrol.wait) before it reads activations.  Contract:
+ *     weight buffers are model constants - no kernel still in flight on the stream writes
+ *     them - and at most one decode launch runs on a device at a time (two concurrent
+ *     streams could each hold part of the SMs at the grid barrier; the bounded wait then
+ *     reports MLXR_ERR_TIMEOUT through mlxr_stream_status).
+ *   MLXR_DECODE_LAUNCH_COOPERATIVE: cooperative launch, no overlap, no contract. */
+enum { MLXR_DECODE_LAUNCH_COOPERATIVE = 0, MLXR_DECODE_LAUNCH_OVERLAPPED = 2 };
+MLXR_API int mlxr_set_decode_launch_mode(int mode);
+
 /* Timeline tracing of the persistent decode kernel (off by default).  dev_ptr: device buffer
  * of 16 uint64 per CTA (148 * 16 * 8 bytes is enough), or NULL to switch tracing off.  Each
  * CTA stores %globaltimer (ns) at: [0] start, [1] x prologue done, [2] first weight stage

@@ -364,6 +364,16 @@ int mlxr_mlp_block_dense(const void* x, const void* w_gate, const void* w_up, co
   return launch_linear_dense(gbuf, w_down, bias_down, y, M, hidden, inter, dtype, st);
 }
 
+int mlxr_set_decode_launch_mode(int mode) {
+  if (mode != MLXR_DECODE_LAUNCH_COOPERATIVE && mode != MLXR_DECODE_LAUNCH_OVERLAPPED)
+  {
+    set_error("mlxr_set_decode_launch_mode: unknown mode %d", mode);
+    return MLXR_ERR_INVALID_ARGUMENT;
+  }
+  set_decode_launch_mode(mode);
+  return MLXR_OK;
+}
+
 int mlxr_debug_set_trace_buffer(void* dev_ptr) {
   set_decode_trace(dev_ptr);
   return MLXR_OK;

@@ -16,6 +16,8 @@ using namespace decode;
 
 static unsigned long long* g_trace = nullptr;  // set by mlxr_debug_set_trace_buffer
 void set_decode_trace(void* p) { g_trace = (unsigned long long*)p; }
+static int g_launch_mode = MLXR_DECODE_LAUNCH_OVERLAPPED;
+void set_decode_launch_mode(int mode) { g_launch_mode = mode; }
 static int g_num_sms = 0;
 static int g_max_smem = 0;
 
@@ -108,14 +110,23 @@ static int launch_inst(const Params& P, const SmemPlan& plan, int G, bool cooper
     MLXR_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g_max_smem));
     attr_done[dev & 63] = true;
   }
-  if (cooperative) {
-    void* args[] = {(void*)&P, (void*)&plan};
-    MLXR_CUDA_TRY(cudaLaunchCooperativeKernel((void*)kern, dim3(G), dim3(kThreads), args, (size_t)plan.total, st));
-    count_launch();
-  } else {
-    kern<<<G, kThreads, plan.total, st>>>(P, plan);
-    MLXR_LAUNCH_CHECK("decode_kernel");
-  }
+  // launch mode (tuning override): 0 cooperative, 1 plain, 2 plain with programmatic overlap
+  int mode = g_launch_mode;
+  (void)cooperative;
+  if (const char* e = getenv("MLXR_DEC_LAUNCH")) mode = atoi(e);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(G);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = (size_t)plan.total;
+  cfg.stream = st;
+  cudaLaunchAttribute at[2];
+  int na = 0;
+  if (mode == 0 || mode == 3) { at[na].id = cudaLaunchAttributeCooperative; at[na].val.cooperative = 1; na++; }
+  if (mode >= 2) { at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[na].val.programmaticStreamSerializationAllowed = 1; na++; }
+  cfg.attrs = at;
+  cfg.numAttrs = na;
+  MLXR_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, P, plan));
+  count_launch();
   return MLXR_OK;
 }
 

@@ -782,6 +782,14 @@ decode_kernel(const __grid_constant__ Params Pg, const __grid_constant__ SmemPla
       if (++i_tile >= i_tl.count) { i_phs++; enter_phase(); }
     }
   };
+  // The weight stream starts before anything else: weights are constants of the model, so under
+  // programmatic overlap their copies may run while the previous kernel of the stream drains.
+  enter_phase();
+  for (int i = 0; i < D; i++) issue();
+  // Everything below may read what earlier kernels wrote (activations, barrier words, status).
+  // Without the programmatic-overlap launch attribute both instructions are no-ops.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // x (and gamma) of batch 0 for this warp's first segment are requested up front so that
   // their latency overlaps the set-up below
   float pre[8] = {0, 0, 0, 0, 0, 0, 0, 0}, gpre[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -796,8 +804,6 @@ decode_kernel(const __grid_constant__ Params Pg, const __grid_constant__ SmemPla
     }
     have_pre = true;
   }
-  enter_phase();
-  for (int i = 0; i < D; i++) issue();
   const int sh1 = c < 2 ? 12 * c : 24, sh2 = c == 3 ? 12 : 0;   // bit position of (scale, min) pair c
 
   int qg = 0;  // sequence number of the tile within this group (indexes the hand-over slots)

@@ -44,6 +44,7 @@ struct DecodeLinear {
 };
 constexpr size_t kDecodeScratchBytes = (size_t)8 << 20;  // split-K partial sums
 void set_decode_trace(void* dev_ptr);
+void set_decode_launch_mode(int mode);
 bool decode_supported(int qt, int M, int K, const void* const* w, int nmat);
 int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype, void* scratch,
                   size_t scratch_bytes, uint32_t* sync, uint32_t* bar_host, int* status, cudaStream_t st);

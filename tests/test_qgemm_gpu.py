@@ -11,7 +11,9 @@ pytestmark = pytest.mark.gpu
 
 TOL = 2e-2
 DT = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
-DT_TIGHT = {"f16": 2e-3, "bf16": 1e-2, "f32": 1e-4}
+# f32 is looser than its rounding: the decode kernel carries activations as 16-bit fixed point
+# per 256-element block (about 2e-4 relative), still far inside the 2e-2 gate.
+DT_TIGHT = {"f16": 2e-3, "bf16": 1e-2, "f32": 1e-3}
 
 
 def _run(oracle, qt, M, N, K, dt, bias=False, seed=0):
