@@ -176,6 +176,14 @@ MLXR_API int mlxr_mlp_block(const void* x, const void* norm_weight, const void* 
                             int hidden, int inter, int quant_type, float eps, int dtype,
                             void* stream);
 
+/* The same block with the down projection's sums stored unrounded as float [M, hidden]:
+ * one rank's partial result when `inter` is this rank's share of the intermediate dimension
+ * (w_gate/w_up hold its rows, w_down its K range).  Extension; the reference has no sharded path. */
+MLXR_API int mlxr_mlp_block_partial_f32(const void* x, const void* norm_weight, const void* w_gate,
+                                        const void* w_up, const void* w_down, float* y_partial,
+                                        int M, int hidden, int inter, int quant_type, float eps,
+                                        int dtype, void* stream);
+
 /* The same block with DENSE weights of the activation dtype and optional biases: the exact
  * signature of swiglu_mlp() (swiglu_mlp_primitive.h:169-176), i.e.
  * SwiGLUMLPPrimitive::eval_cpu (swiglu_mlp_primitive.mm:47-82).  w_gate, w_up:

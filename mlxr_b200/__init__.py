@@ -10,7 +10,7 @@ the shared library exists.
 """
 from .types import QuantType, RoPEScalingMode  # noqa: F401
 
-_OPS = ("compute_quantized_weight_size", "compute_rope_tables", "dequantize", "mlp_block", "q_gemm_dequant",
+_OPS = ("compute_quantized_weight_size", "compute_rope_tables", "dequantize", "mlp_block", "mlp_block_partial", "q_gemm_dequant",
         "qkv_rope", "quant_type_name", "rmsnorm_fused", "rope_apply", "swiglu", "swish", "swiglu_mlp")
 
 
@@ -18,7 +18,7 @@ def __getattr__(name):
     if name in _OPS:
         from . import ops
         return getattr(ops, name)
-    if name in ("ops", "_capi", "quantize", "build", "build_cpp"):
+    if name in ("ops", "_capi", "quantize", "build", "build_cpp", "tp"):
         import importlib
         return importlib.import_module(f".{name}", __name__)
     raise AttributeError(f"module 'mlxr_b200' has no attribute {name!r}")

@@ -41,6 +41,7 @@ PROTOTYPES = {
     "mlxr_swiglu": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
     "mlxr_rope_apply": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp]),
     "mlxr_mlp_block": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp]),
+    "mlxr_mlp_block_partial_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp]),
     "mlxr_mlp_block_dense": (_i, [_vp] * 8 + [_i, _i, _i, _i, _vp]),
     "mlxr_stream_status": (_i, [_vp, _vp]),
     "mlxr_debug_set_trace_buffer": (_i, [_vp]),
@@ -51,7 +52,20 @@ PROTOTYPES = {
     "mlxr_release_workspaces": (_i, []),
 }
 
-for _name, (_res, _args) in PROTOTYPES.items():
+# every symbol include/mlxr_b200_tp.h declares
+TP_PROTOTYPES = {
+    "mlxr_tp_unique_id": (_i, [_vp]),
+    "mlxr_tp_create": (_i, [_vp, _i, _i, _i, C.POINTER(_vp)]),
+    "mlxr_tp_destroy": (_i, [_vp]),
+    "mlxr_tp_rank": (_i, [_vp]),
+    "mlxr_tp_world": (_i, [_vp]),
+    "mlxr_tp_shard_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "mlxr_tp_pack_shard": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i]),
+    "mlxr_tp_mlp_block": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp]),
+    "mlxr_tp_all_reduce": (_i, [_vp, _vp, _vp, _sz, _i, _i, _vp]),
+}
+
+for _name, (_res, _args) in list(PROTOTYPES.items()) + list(TP_PROTOTYPES.items()):
     _fn = getattr(lib, _name)  # AttributeError here = library out of date with the header
     _fn.restype = _res
     _fn.argtypes = _args

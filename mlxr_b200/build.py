@@ -91,7 +91,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             f.write("\n".join(log_lines) + "\n")
     if jobs or not os.path.exists(LIB):
         cmd = [nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
-               "-Xlinker", "--no-undefined"]
+               "-Xlinker", "--no-undefined", "-ldl"]
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode != 0:
             sys.stderr.write(p.stdout + p.stderr)

@@ -82,6 +82,13 @@ int get_workspace(cudaStream_t st, size_t need, Workspace** out, size_t need_sta
   return MLXR_OK;
 }
 
+int stream_status_word(cudaStream_t st, int** status) {
+  Workspace* ws = nullptr;
+  if (int r = get_workspace(st, 0, &ws)) return r;
+  *status = ws->status;
+  return MLXR_OK;
+}
+
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // ---- validation helpers ----------------------------------------------------------------
@@ -304,9 +311,11 @@ int mlxr_rope_apply(const void* x, const uint16_t* cos_f16, const uint16_t* sin_
   return MLXR_OK;
 }
 
-int mlxr_mlp_block(const void* x, const void* norm_weight, const void* w_gate, const void* w_up,
-                   const void* w_down, void* y, int M, int hidden, int inter, int qt, float eps,
-                   int dtype, void* stream) {
+// y_f32: y is float [M, hidden] and receives the unrounded sums (a rank's partial result of a
+// tensor-parallel block); otherwise y has the activation dtype.
+static int mlp_block_impl(const void* x, const void* norm_weight, const void* w_gate, const void* w_up,
+                          const void* w_down, void* y, int M, int hidden, int inter, int qt, float eps,
+                          int dtype, bool y_f32, void* stream) {
   if (int r = check_dtype(dtype)) return r;
   if (M < 0 || hidden <= 0 || inter <= 0) { set_error("Input must be 2D [M, hidden_size]"); return MLXR_ERR_INVALID_ARGUMENT; }
   if (int r = check_quant(qt, hidden, 0, false)) return r;
@@ -329,6 +338,7 @@ int mlxr_mlp_block(const void* x, const void* norm_weight, const void* w_gate, c
     L[0].interleave = 1; L[0].K = hidden; L[0].x = x; L[0].gamma = norm_weight; L[0].eps = eps;
     L[0].y[0] = base;  // h [M, inter], lives in L2 between the phases
     L[1].w[0] = w_down; L[1].rows[0] = hidden; L[1].nmat = 1; L[1].K = inter; L[1].x = base; L[1].y[0] = y;
+    if (y_f32) L[1].epi[0] = 3;
     return launch_decode(L, 2, M, qt, dtype, ws->buf, kDecodeScratchBytes, ws->sync, &ws->bar_host, ws->status, st);
   }
   void* nbuf = base;
@@ -342,7 +352,22 @@ int mlxr_mlp_block(const void* x, const void* norm_weight, const void* w_gate, c
   if (int r = run_linear(n, w_gate, nullptr, gbuf, M, inter, hidden, qt, dtype, st)) return r;
   if (int r = run_linear(n, w_up, nullptr, ubuf, M, inter, hidden, qt, dtype, st)) return r;
   if (int r = launch_swiglu(gbuf, ubuf, gbuf, (size_t)M * inter, dtype, st)) return r;
-  return run_linear(gbuf, w_down, nullptr, y, M, hidden, inter, qt, dtype, st);
+  if (!y_f32) return run_linear(gbuf, w_down, nullptr, y, M, hidden, inter, qt, dtype, st);
+  // generic path: the linear rounds to the activation dtype before the widening cast
+  if (int r = run_linear(gbuf, w_down, nullptr, nbuf, M, hidden, inter, qt, dtype, st)) return r;
+  return launch_cast_to_f32(nbuf, (float*)y, (size_t)M * hidden, dtype, st);
+}
+
+int mlxr_mlp_block(const void* x, const void* norm_weight, const void* w_gate, const void* w_up,
+                   const void* w_down, void* y, int M, int hidden, int inter, int qt, float eps,
+                   int dtype, void* stream) {
+  return mlp_block_impl(x, norm_weight, w_gate, w_up, w_down, y, M, hidden, inter, qt, eps, dtype, false, stream);
+}
+
+int mlxr_mlp_block_partial_f32(const void* x, const void* norm_weight, const void* w_gate, const void* w_up,
+                               const void* w_down, float* y_partial, int M, int hidden, int inter, int qt,
+                               float eps, int dtype, void* stream) {
+  return mlp_block_impl(x, norm_weight, w_gate, w_up, w_down, y_partial, M, hidden, inter, qt, eps, dtype, true, stream);
 }
 
 int mlxr_mlp_block_dense(const void* x, const void* w_gate, const void* w_up, const void* w_down,

@@ -49,7 +49,7 @@ __host__ __device__ inline int block_bytes(int qt) {
 
 // The 16 NF4 levels (same literals as the oracle's table).
 __device__ __constant__ static const float kNF4[16] = {
-#include "../../oracle/nf4_codebook.inc"
+#include "nf4_codebook.inc"
 };
 
 // ---- activation dtype traits --------------------------------------------------------

@@ -49,7 +49,7 @@ constexpr int kSlots = 3;                               // tiles in flight per g
 constexpr int kMaxStages = 6;
 constexpr uint32_t kSpinLimit = 1u << 22;
 
-enum Epilogue { kEpiPlain = 0, kEpiRope = 2 };
+enum Epilogue { kEpiPlain = 0, kEpiRope = 2, kEpiF32 = 3 };   // kEpiF32: fp32 store (partial sums of a sharded linear)
 
 struct Phase {
   // weights: up to three packed matrices stacked along N, or gate/up interleaved in tiles
@@ -649,6 +649,12 @@ __device__ __forceinline__ void tile_epilogue(const Params& P, const Phase& ph, 
       float ve = tile[(2 * jj) * MB + m], vo = tile[(2 * jj + 1) * MB + m];
       const T* bias = reinterpret_cast<const T*>(ph.bias[mat]);
       if (bias) { ve += Act<T>::to_f(bias[R]); if (has_odd) vo += Act<T>::to_f(bias[R + 1]); }
+      if (ph.epi[mat] == kEpiF32) {
+        float* of = reinterpret_cast<float*>(ph.y[mat]) + (size_t)m * ph.rows[mat] + R;
+        of[0] = ve;
+        if (has_odd) of[1] = vo;
+        continue;
+      }
       T* out = reinterpret_cast<T*>(ph.y[mat]) + (size_t)m * ph.rows[mat] + R;
       if (ph.epi[mat] == kEpiRope) {
         const float qe = Act<T>::to_f(Act<T>::from_f(ve)), qo = Act<T>::to_f(Act<T>::from_f(vo));

@@ -93,6 +93,35 @@ int launch_swiglu(const void* g, const void* u, void* o, size_t n, int dtype, cu
   return MLXR_OK;
 }
 
+// ---- widening cast (partial sums of a sharded linear on the generic path) ------------------
+template <typename T>
+__global__ void __launch_bounds__(256) cast_f32_kernel(const T* __restrict__ x, float* __restrict__ y, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) y[i] = Act<T>::to_f(x[i]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) cast_from_f32_kernel(const float* __restrict__ x, T* __restrict__ y, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) y[i] = Act<T>::from_f(x[i]);
+}
+
+int launch_cast_from_f32(const float* x, void* y, size_t n, int dtype, cudaStream_t st) {
+  if (n == 0) return MLXR_OK;
+  size_t blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  MLXR_DISPATCH_DTYPE(dtype, T, { cast_from_f32_kernel<T><<<(int)blocks, 256, 0, st>>>(x, (T*)y, n); });
+  MLXR_LAUNCH_CHECK("cast_from_f32_kernel");
+  return MLXR_OK;
+}
+
+int launch_cast_to_f32(const void* x, float* y, size_t n, int dtype, cudaStream_t st) {
+  if (n == 0) return MLXR_OK;
+  size_t blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  MLXR_DISPATCH_DTYPE(dtype, T, { cast_f32_kernel<T><<<(int)blocks, 256, 0, st>>>((const T*)x, y, n); });
+  MLXR_LAUNCH_CHECK("cast_f32_kernel");
+  return MLXR_OK;
+}
+
 // ---- RoPE ------------------------------------------------------------------------------
 // One thread per (token, head, pair): interleaved pairs (2p, 2p+1), binary16 tables, fp32
 // math, one rounding at the store (rope_apply.metal:103-172).  A token whose position

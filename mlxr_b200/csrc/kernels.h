@@ -17,6 +17,10 @@ int launch_linear_dense(const void* x, const void* w, const void* bias, void* y,
                         int dtype, cudaStream_t st);
 int launch_rmsnorm(const void* x, const void* w, const void* res, void* y, int rows, int hidden,
                    float eps, int dtype, cudaStream_t st);
+// device status word of the (device, stream) workspace: kernels record time-outs there
+int stream_status_word(cudaStream_t st, int** status);
+int launch_cast_from_f32(const float* x, void* y, size_t n, int dtype, cudaStream_t st);
+int launch_cast_to_f32(const void* x, float* y, size_t n, int dtype, cudaStream_t st);
 int launch_swiglu(const void* g, const void* u, void* o, size_t n, int dtype, cudaStream_t st);
 int launch_rope(const void* x, const uint16_t* cos_t, const uint16_t* sin_t,
                 const int32_t* positions, void* y, size_t tokens, int heads, int head_dim,
@@ -36,7 +40,7 @@ struct DecodeLinear {
   float eps;
   void* y[3];
   const void* bias[3];
-  int epi[3];              // 0 plain, 2 RoPE
+  int epi[3];              // 0 plain, 2 RoPE, 3 plain fp32 store (y is float*)
   const uint16_t* cos_t;
   const uint16_t* sin_t;
   const int32_t* positions;

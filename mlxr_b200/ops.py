@@ -213,6 +213,22 @@ def mlp_block(x: torch.Tensor, norm_weight: Optional[torch.Tensor], w_gate: torc
     return y
 
 
+def mlp_block_partial(x: torch.Tensor, norm_weight: Optional[torch.Tensor], w_gate_shard: torch.Tensor,
+                      w_up_shard: torch.Tensor, w_down_shard: torch.Tensor, inter_local: int,
+                      quant_type: QuantType, eps: float = 1e-5) -> torch.Tensor:
+    """One rank's float32 partial [M, hidden] of the tensor-parallel block (see
+    mlxr_mlp_block_partial_f32): `inter_local` is the rank's share of the intermediate size."""
+    if x.dim() != 2:
+        raise _capi.MlxrInvalidArgument(_capi.ERR_INVALID_ARGUMENT, "Input must be 2D [M, hidden_size]")
+    M, hidden = x.shape
+    y = torch.empty((M, hidden), dtype=torch.float32, device=x.device)
+    check(lib.mlxr_mlp_block_partial_f32(_dev(x, "x"), _dev(norm_weight, "norm_weight"),
+                                         _dev(w_gate_shard, "w_gate_shard"), _dev(w_up_shard, "w_up_shard"),
+                                         _dev(w_down_shard, "w_down_shard"), y.data_ptr(), M, hidden, inter_local,
+                                         int(quant_type), eps, _dtype_code(x), _stream()))
+    return y
+
+
 def qkv_rope(x: torch.Tensor, norm_weight: Optional[torch.Tensor], wq: torch.Tensor,
              wk: torch.Tensor, wv: torch.Tensor, cos_table: torch.Tensor, sin_table: torch.Tensor,
              positions: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int,

@@ -179,6 +179,20 @@ def mlp_block(x, norm_w, wg, wu, wd, inter: int, qt: int, eps: float, dtype: int
     return round_to(linear(h, wd, hidden, qt), dtype)
 
 
+def mlp_block_partial(x, norm_w, wg_s, wu_s, wd_s, inter_local: int, qt: int, eps: float, dtype: int) -> np.ndarray:
+    """One rank's unrounded partial of the tensor-parallel block: the shard's gate/up rows give
+    its slice of h (rounded to `dtype` like the whole h), the shard of down multiplies it; the
+    float32 sums are returned as they are.  Summed over ranks and rounded, this is mlp_block up
+    to float32 summation order."""
+    x = _f32(x)
+    hidden = x.shape[1]
+    n = round_to(rmsnorm(x, norm_w, eps), dtype) if norm_w is not None else x
+    g = round_to(linear(n, wg_s, inter_local, qt), dtype)
+    u = round_to(linear(n, wu_s, inter_local, qt), dtype)
+    h = round_to(swiglu(g, u), dtype)
+    return linear(h, wd_s, hidden, qt)
+
+
 def mlp_block_f64(x, norm_w, wg, wu, wd, inter: int, qt: int, eps: float) -> np.ndarray:
     """Same chain in float64 with no intermediate rounding: the 'truth' both the fp32
     oracle and the GPU are measured against in the relative-L2 gate."""
