@@ -35,7 +35,11 @@ sys.path.insert(0, ROOT)
 
 import numpy as np  # noqa: E402
 
-H, I = 4096, 14336
+H, I = 4096, 14336            # Llama-3-8B MLP (the default workload)
+SIZES = {"hidden": H, "inter": I}
+# DRAM bytes (read + write) of one decode_kernel launch from an ncu capture of this workload,
+# keyed by (hidden, inter, batch); see profiles/
+TRAFFIC = {(4096, 14336, 1): 103057920}
 QT_Q4_K = 3
 EPS = 1e-5
 SEED = 1234
@@ -119,11 +123,12 @@ class ClockSampler:
 
 
 def cpu_baseline(M: int, budget_s: float = 20.0):
+    H, I = SIZES["hidden"], SIZES["inter"]
     """Oracle port of the reference CPU path (QGemmDequantPrimitive::eval_cpu: full dequant to
     fp32, then the scalar m/n/k loop, single thread) for the whole MLP block at batch M,
     repeated while the time budget lasts."""
     from oracle import oracle as O
-    wg, wu, wd, x, gamma = make_inputs(M)
+    wg, wu, wd, x, gamma = make_inputs(M, H, I)
     xb = O.round_to(x, O.BF16)
     gb = O.round_to(gamma, O.BF16)
 
@@ -158,18 +163,25 @@ def run_reference(args):
         "impl": "reference", "metric": "mlp_decode_tokens_per_s", "value": cb["value"], "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": config_dict(M, args.gpus, 0),
+        "config": config_dict(M, 1, 0),
         "cpu_baseline": cb,
         "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
 
 
-def config_dict(M, n_gpus, copies):
-    return {"workload": f"Llama-3-8B-shaped Q4_K decode MLP block (hidden {H}, intermediate {I}, RMSNorm prologue, "
-                        f"SwiGLU), batch {M}, bf16 activations",
-            "batch": M, "quant": "Q4_K (MLXR layout)", "parallelism": "single GPU" if n_gpus == 1 else f"tp{n_gpus}",
-            "l2": f"weights rotate over {copies} device copies ({copies * 99} MB > 126 MB L2)"}
+def config_dict(M, n_gpus, copies, exchange=None):
+    H, I = SIZES["hidden"], SIZES["inter"]
+    name = {(4096, 14336): "Llama-3-8B", (8192, 28672): "Llama-3-70B", (2048, 5632): "TinyLlama"}.get((H, I), "custom")
+    mb = copies * (3 * H * I * 144 // 256) // n_gpus // 1000000
+    d = {"workload": f"{name}-shaped Q4_K decode MLP block (hidden {H}, intermediate {I}, RMSNorm prologue, "
+                     f"SwiGLU), batch {M}, bf16 activations",
+         "batch": M, "quant": "Q4_K (MLXR layout)",
+         "parallelism": "single GPU" if n_gpus == 1 else f"tp{n_gpus} (gate/up rows and down columns sharded, one sum over ranks per step)",
+         "l2": f"weights rotate over {copies} device copies per GPU ({mb} MB per GPU; L2 is 126 MB)"}
+    if exchange:
+        d["exchange"] = exchange
+    return d
 
 
 def run_mine(args):
@@ -187,10 +199,19 @@ def run_mine(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     M = args.batch
     K, W = args.steps, max(args.warmup, 3)
-    copies = 8
+    H, I = SIZES["hidden"], SIZES["inter"]
+    # enough distinct weight copies per GPU that consecutive steps cannot be served from L2
+    shard_mb = 3 * H * I * 144 // 256 // world / 1e6
+    copies = int(min(64, max(8, np.ceil(800.0 / shard_mb))))
 
-    wg, wu, wd, x, gamma = make_inputs(M)
+    wg, wu, wd, x, gamma = make_inputs(M, H, I)
     dev = torch.device("cuda", local)
+    ctx = None
+    exchange = {"auto": 0, "nccl_f32": 1, "nccl_act": 2, "peer": 3}[args.exchange]
+    if world > 1:
+        import mlxr_b200.tp as tp
+        ctx = tp.TPContext()
+        wg, wu, wd = tp.shard_mlp_weights(wg, wu, wd, H, I, QT_Q4_K, rank, world)
     wsets = []
     for _ in range(copies):
         wsets.append(tuple(torch.from_numpy(a).to(dev) for a in (wg, wu, wd)))
@@ -202,29 +223,37 @@ def run_mine(args):
 
     def step(i):
         a, b, c = wsets[i % copies]
-        check(lib.mlxr_mlp_block(xt.data_ptr(), gt.data_ptr(), a.data_ptr(), b.data_ptr(), c.data_ptr(),
-                                 y.data_ptr(), M, H, I, QT_Q4_K, EPS, 1, st))
+        if ctx is None:
+            check(lib.mlxr_mlp_block(xt.data_ptr(), gt.data_ptr(), a.data_ptr(), b.data_ptr(), c.data_ptr(),
+                                     y.data_ptr(), M, H, I, QT_Q4_K, EPS, 1, st))
+        else:
+            check(lib.mlxr_tp_mlp_block(ctx._h, xt.data_ptr(), gt.data_ptr(), a.data_ptr(), b.data_ptr(), c.data_ptr(),
+                                        y.data_ptr(), M, H, I, QT_Q4_K, EPS, 1, exchange, st))
 
     # The K timed steps are captured once into a CUDA graph and replayed: at ~20-30 us per
-    # step a Python/ctypes launch loop would measure the host, not the GPU.
+    # step a Python/ctypes launch loop would measure the host, not the GPU.  The NCCL exchange
+    # modes are timed with plain launches instead (a library collective per step dominates there).
+    use_graph = ctx is None or exchange in (0, 3)
     side = torch.cuda.Stream()
-    graph = torch.cuda.CUDAGraph()
+    graph = torch.cuda.CUDAGraph() if use_graph else None
     with torch.cuda.stream(side):
         st = side.cuda_stream
         for i in range(W):
             step(i)
         side.synchronize()
         l_cap0 = lib.mlxr_launch_count()
-        with torch.cuda.graph(graph, stream=side):
-            st = torch.cuda.current_stream().cuda_stream
-            for i in range(K):
-                step(W + i)
-        launches = lib.mlxr_launch_count() - l_cap0
+        if use_graph:
+            with torch.cuda.graph(graph, stream=side):
+                st = torch.cuda.current_stream().cuda_stream
+                for i in range(K):
+                    step(W + i)
+            launches = lib.mlxr_launch_count() - l_cap0
         st = side.cuda_stream
     sampler = ClockSampler(local)
     sampler.start()
     with torch.cuda.stream(side):
-        graph.replay()          # untimed: first replay uploads the graph
+        if use_graph:
+            graph.replay()          # untimed: first replay uploads the graph
         side.synchronize()
         if world > 1:
             dist.barrier()
@@ -232,7 +261,12 @@ def run_mine(args):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0 = time.perf_counter()
         e0.record(side)
-        graph.replay()
+        if use_graph:
+            graph.replay()
+        else:
+            for i in range(K):
+                step(W + i)
+            launches = lib.mlxr_launch_count() - l_cap0
         e1.record(side)
         side.synchronize()
         t1 = time.perf_counter()
@@ -254,12 +288,22 @@ def run_mine(args):
 
     def step_host(i):
         a, b, c = wsets[i % copies]
-        check(lib.mlxr_mlp_block_host(xh.data_ptr(), gt.data_ptr(), a.data_ptr(), b.data_ptr(), c.data_ptr(),
-                                      yh.data_ptr(), M, H, I, QT_Q4_K, EPS, 1, st))
+        if ctx is None:
+            check(lib.mlxr_mlp_block_host(xh.data_ptr(), gt.data_ptr(), a.data_ptr(), b.data_ptr(), c.data_ptr(),
+                                          yh.data_ptr(), M, H, I, QT_Q4_K, EPS, 1, st))
+        else:
+            # every rank copies the replicated x in, runs its share and the exchange, reads y back
+            xt.copy_(xh, non_blocking=True)
+            check(lib.mlxr_tp_mlp_block(ctx._h, xt.data_ptr(), gt.data_ptr(), a.data_ptr(), b.data_ptr(), c.data_ptr(),
+                                        y.data_ptr(), M, H, I, QT_Q4_K, EPS, 1, exchange, st))
+            yh.copy_(y, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
 
     for i in range(W):
         step_host(i)
     torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
     Ke = min(K, 2000)
     th0 = time.perf_counter()
     for i in range(Ke):
@@ -278,7 +322,8 @@ def run_mine(args):
 
     if rank == 0:
         hbm, _, which = measured_peaks()
-        ab = algorithmic_bytes(M)
+        # per GPU: its share of the weights plus the replicated activations
+        ab = (algorithmic_bytes(M, H, I) - 2 * M * H * 2 - H * 2) // world + 2 * M * H * 2 + H * 2
         achieved = ab / (ms_step * 1e-3) / 1e9
         cb = None
         if world == 1 and not args.no_cpu:
@@ -287,18 +332,22 @@ def run_mine(args):
             "metric": "mlp_decode_tokens_per_s", "value": M / (ms_step * 1e-3),
             "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": config_dict(M, world, copies),
+            "config": config_dict(M, world, copies, args.exchange if world > 1 else None),
             "e2e": {"value": M / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": M * H * 2, "d2h_bytes_per_step": M * H * 2,
                     "ms_per_step": e2e_s * 1e3},
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                         "traffic": None, "peak_source": which, "algorithmic_bytes_per_step": ab,
-                         "kernel": "decode_kernel (one persistent launch per step: RMSNorm + gate/up + SwiGLU + down)",
-                         "timing": "CUDA events around a CUDA-graph replay of the K steps"},
+                         "traffic": TRAFFIC.get((H, I, M)) if world == 1 else None, "peak_source": which,
+                         "algorithmic_bytes_per_step": ab, "per": "GPU",
+                         "kernel": "decode_kernel (one persistent launch per step: RMSNorm + gate/up + SwiGLU + down)"
+                                   + ("" if world == 1 else " + tp_exchange_kernel"),
+                         "timing": "CUDA events around " + ("a CUDA-graph replay of the K steps" if use_graph else "K plain launches")},
             "cpu_baseline": cb,
         }
         print(json.dumps(line))
+    if ctx is not None:
+        ctx.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -312,7 +361,12 @@ def main():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--hidden", type=int, default=H)
+    ap.add_argument("--inter", type=int, default=I)
+    ap.add_argument("--exchange", default="auto", choices=["auto", "nccl_f32", "nccl_act", "peer"],
+                    help="how the ranks' partial sums are added (N > 1)")
     args = ap.parse_args()
+    SIZES["hidden"], SIZES["inter"] = args.hidden, args.inter
     if args.impl == "reference":
         run_reference(args)
     else:
