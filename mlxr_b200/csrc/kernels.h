@@ -53,4 +53,9 @@ bool decode_supported(int qt, int M, int K, const void* const* w, int nmat);
 int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype, void* scratch,
                   size_t scratch_bytes, uint32_t* sync, uint32_t* bar_host, int* status, cudaStream_t st);
 
+// ---- tensor-core GEMM for batch >= 9 on Q4_K with 16-bit activations (prefill.cu) -------------
+bool prefill_supported(int qt, int M, int N, int K, int dtype, const void* x, const void* w, const void* y);
+int launch_prefill(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int qt, int dtype,
+                   int* status, cudaStream_t st);
+
 }  // namespace mlxr

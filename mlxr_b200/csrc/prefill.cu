@@ -1,0 +1,449 @@
+// Prefill / large-batch quantized GEMM on the 5th-generation tensor cores:
+//   Y[M, N] = X[M, K] * dequant(W[N, K])^T (+ bias),  W packed Q4_K, X and Y fp16 or bf16.
+//
+// One CTA computes a (MT x 128) x 256 output tile over the whole K:
+//   * X tiles (128 rows x 64 K, 16 KB each) arrive by 2-D tensor TMA with the 128-byte swizzle;
+//   * eight producer warps read the packed Q4_K rows (one weight row per thread), dequantize
+//     with the reference shader's half arithmetic (q_gemm_dequant.metal:214-259; bit-exact
+//     fp16 values), round to the activation dtype and store them as the K-major, 128-byte
+//     swizzled B tile (256 rows x 64 K, 32 KB);
+//   * one thread issues tcgen05.mma (cta_group::1, 128 x 256 x 16, fp32 accumulators in tensor
+//     memory); the same B tile feeds MT accumulators (MT x 256 columns of TMEM), which halves
+//     the dequantization work per flop at MT = 2;
+//   * the producer warps drain the accumulators with tcgen05.ld and store Y.
+// Stages are recycled through mbarriers; tcgen05.commit releases a stage when the MMAs that
+// read it have finished.  Every wait is bounded: when one gives up, a flag makes all roles leave
+// their loops, the TMA thread waits (bounded) for its copies in flight, tensor memory is freed
+// and the stream's status word reports MLXR_ERR_TIMEOUT.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace mlxr {
+namespace prefill {
+
+constexpr int kBM = 128;          // rows of X per accumulator (MMA M)
+constexpr int kBN = 256;          // weight rows per tile (MMA N)
+constexpr int kBK = 64;           // K per stage: one 128-byte swizzle row of 16-bit elements
+constexpr int kUmmaK = 16;
+constexpr int kProducerWarps = 8; // one weight row per producer thread
+constexpr int kThreads = (2 + kProducerWarps) * 32;
+constexpr int kATile = kBM * kBK * 2;     // 16 KB
+constexpr int kBTile = kBN * kBK * 2;     // 32 KB
+constexpr uint32_t kSpin = 1u << 22;
+
+struct Params {
+  const uint8_t* w;
+  const void* bias;
+  void* y;
+  int M, N, K;
+  size_t row_bytes;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait; false when it gave up or another role already did.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* dead) {
+  for (uint32_t i = 0; i < kSpin; i++) {
+    if (mbar_try(bar, parity)) return true;
+    if ((i & 255u) == 255u && *dead) return false;
+  }
+  *dead = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+// ---- tcgen05 wrappers ----------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrive on an mbarrier once every MMA issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns: thread i of the warp receives lane (base + i)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile with the 128-byte swizzle: rows are 128
+// bytes, groups of 8 rows are 1024 bytes apart (stride byte offset), descriptor version 1
+// (sm_100), layout type 2 (SWIZZLE_128B).  The tile base is 1024-byte aligned; a K step of 16
+// elements inside the swizzle row advances the start address by 32 bytes.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);        // start address, bits 0-13
+  d |= (uint64_t)0 << 16;                         // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024u >> 4) << 32;              // stride byte offset, bits 32-45
+  d |= (uint64_t)1 << 46;                         // descriptor version
+  d |= (uint64_t)2 << 61;                         // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor of kind::f16: fp32 accumulate, A and B of format `fmt` (0 fp16, 1 bf16),
+// both K-major, N and M of the MMA.
+__host__ __device__ constexpr uint32_t instr_desc(int fmt, int m, int n) {
+  return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <typename T> struct Fmt;
+template <> struct Fmt<__half> { static constexpr int v = 0; };
+template <> struct Fmt<__nv_bfloat16> { static constexpr int v = 1; };
+
+// two reference-exact fp16 weights -> one 32-bit pair of the activation dtype
+template <typename T>
+__device__ __forceinline__ uint32_t pack_pair(__half2 v) {
+  if constexpr (sizeof(T) == 2 && Fmt<T>::v == 0) {
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    const float2 f = __half22float2(v);
+    __nv_bfloat162 b = __float22bfloat162_rn(f);
+    return *reinterpret_cast<uint32_t*>(&b);
+  }
+}
+
+// Eight consecutive weights of a Q4_K sub-block (one 32-bit word of nibbles, element order =
+// nibble order) -> four packed pairs.  1024 + n as fp16 is 0x6400 | n; subtracting 1032 gives
+// n - 8 exactly; then the shader's two roundings: rn16(rn16((n - 8) * ss) + sm).
+template <typename T>
+__device__ __forceinline__ uint4 dequant8(uint32_t v, __half2 ss, __half2 sm) {
+  const uint32_t lo = v & 0x0F0F0F0Fu, hi = (v >> 4) & 0x0F0F0F0Fu;
+  const __half2 off = __half2half2(__ushort_as_half((unsigned short)0x6408));   // 1032
+  uint32_t out[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    const uint32_t sel = (uint32_t)j | ((uint32_t)j << 4) | ((uint32_t)(4 + j) << 8) | ((uint32_t)(4 + j) << 12);
+    uint32_t bits = (__byte_perm(lo, hi, sel) & 0x00FF00FFu) | 0x64006400u;
+    const __half2 q = __hsub2(*reinterpret_cast<__half2*>(&bits), off);
+    const __half2 r = __hadd2_rn(__hmul2_rn(q, ss), sm);
+    out[j] = pack_pair<T>(r);
+  }
+  return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+struct Shared {
+  uint64_t full_a[4];
+  uint64_t full_b[4];
+  uint64_t empty[4];
+  uint64_t acc_full;
+  uint32_t tmem_base;
+  int dead;
+};
+
+// MT accumulators (MT x 128 rows of X) per CTA, STAGES pipeline stages.
+template <typename T, int MT, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
+  extern __shared__ uint8_t smem_raw[];
+  // tiles need 1024-byte alignment for the 128-byte swizzle
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  constexpr int kStageBytes = MT * kATile + kBTile;
+  Shared* sh = reinterpret_cast<Shared*>(smem + (size_t)STAGES * kStageBytes);
+  volatile int* dead = &sh->dead;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * (MT * kBM);
+  const int nkb = P.K / kBK;
+  constexpr uint32_t kCols = MT * kBN;        // TMEM columns (256 or 512: powers of two)
+
+  if (tid == 0) {
+    sh->dead = 0;
+    for (int s = 0; s < STAGES; s++) {
+      mbar_init(smem_u32(&sh->full_a[s]), 1);
+      mbar_init(smem_u32(&sh->full_b[s]), kProducerWarps);
+      mbar_init(smem_u32(&sh->empty[s]), 1);
+    }
+    mbar_init(smem_u32(&sh->acc_full), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&sh->tmem_base), kCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&sh->tmem_base);
+
+  if (warp == 0) {
+    // ===== TMA producer of the X tiles =====
+    if (lane == 0) {
+      int issued = 0;
+      for (int kb = 0; kb < nkb; kb++) {
+        const int s = kb % STAGES, it = kb / STAGES;
+        if (!mbar_wait(smem_u32(&sh->empty[s]), (it & 1) ^ 1, dead)) break;
+        const uint32_t bar = smem_u32(&sh->full_a[s]);
+        mbar_expect_tx(bar, MT * kATile);
+#pragma unroll
+        for (int a = 0; a < MT; a++)
+          tma_load_2d(smem_u32(smem + (size_t)s * kStageBytes + a * kATile), &xmap, kb * kBK, m0 + a * kBM, bar);
+        issued = kb + 1;
+      }
+      if (*dead) {
+        // copies in flight must land before the CTA may exit (bounded)
+        for (int kb = max(0, issued - STAGES); kb < issued; kb++) {
+          const uint32_t bar = smem_u32(&sh->full_a[kb % STAGES]);
+          for (uint32_t i = 0; i < kSpin; i++) if (mbar_try(bar, (kb / STAGES) & 1)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===== MMA issuer =====
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(Fmt<T>::v, kBM, kBN);
+      bool ok = true;
+      for (int kb = 0; kb < nkb && ok; kb++) {
+        const int s = kb % STAGES, it = kb / STAGES;
+        ok = mbar_wait(smem_u32(&sh->full_a[s]), it & 1, dead) && mbar_wait(smem_u32(&sh->full_b[s]), it & 1, dead);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_base = smem_u32(smem + (size_t)s * kStageBytes);
+        const uint32_t b_base = a_base + MT * kATile;
+#pragma unroll
+        for (int k = 0; k < kBK / kUmmaK; k++) {
+          const uint64_t bdesc = smem_desc_sw128(b_base + k * kUmmaK * 2);
+#pragma unroll
+          for (int a = 0; a < MT; a++) {
+            const uint64_t adesc = smem_desc_sw128(a_base + a * kATile + k * kUmmaK * 2);
+            umma_f16(tmem + a * kBN, adesc, bdesc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+        }
+        umma_commit(smem_u32(&sh->empty[s]));      // the stage is free when these MMAs are done
+      }
+      if (ok) umma_commit(smem_u32(&sh->acc_full));
+    }
+  } else {
+    // ===== dequantizing producers: thread p owns weight row n0 + p =====
+    const int p = tid - 64;
+    const int n = n0 + p;
+    const bool live = n < P.N;
+    const uint8_t* rowp = P.w + (size_t)(live ? n : 0) * P.row_bytes;
+    uint4 q0 = make_uint4(0, 0, 0, 0), q1 = q0, hdr = q0;
+    auto fetch = [&](int kb) {
+      // k-block kb: super-block kb / 4, sub-blocks 2 * (kb % 4) and the next one
+      const uint8_t* blk = rowp + (size_t)(kb >> 2) * 144;
+      if ((kb & 3) == 0) hdr = __ldg(reinterpret_cast<const uint4*>(blk));
+      q0 = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * (kb & 3)));
+      q1 = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * (kb & 3)));
+    };
+    if (live) fetch(0);
+    for (int kb = 0; kb < nkb; kb++) {
+      const int s = kb % STAGES, it = kb / STAGES;
+      const uint4 c0 = q0, c1 = q1, ch = hdr;
+      if (live && kb + 1 < nkb) fetch(kb + 1);
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->empty[s]), (it & 1) ^ 1, dead))) break;   // warp-uniform
+      uint8_t* brow = smem + (size_t)s * kStageBytes + MT * kATile + (size_t)p * 128;
+      uint4 o[8];
+      if (live) {
+        // header: d, dmin (fp16), scales[12] -> (scale, min) of the two sub-blocks
+        const __half d = __ushort_as_half((unsigned short)(ch.x & 0xFFFFu));
+        const __half dmin = __ushort_as_half((unsigned short)(ch.x >> 16));
+        // scales[3g .. 3g+2] of group g = (kb & 3) >> 1 as one 24-bit value (only scales[0..5] are read)
+        const uint32_t t24 = (kb & 2) ? ((ch.y >> 24) | ((ch.z & 0xFFFFu) << 8)) : (ch.y & 0xFFFFFFu);
+        const uint32_t w8[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+        for (int sb = 0; sb < 2; sb++) {
+          // sub-block offset o = (2 * (kb & 3) + sb) & 3: only o == 1 takes the second pair
+          // (offsets 2 and 3 alias offset 0, q_gemm_dequant.metal:222-242)
+          int sc, mn;
+          const uint32_t b0 = t24 & 0xFFu, b1 = (t24 >> 8) & 0xFFu, b2 = (t24 >> 16) & 0xFFu;
+          if (((kb & 1) == 0) && sb == 1) {
+            sc = (int)(((b1 >> 4) | ((b2 & 0x03u) << 4)) & 0x3Fu);
+            mn = (int)((b2 >> 2) & 0x3Fu);
+          } else {
+            sc = (int)(b0 & 0x3Fu);
+            mn = (int)(((b0 >> 6) | ((b1 & 0x0Fu) << 2)) & 0x3Fu);
+          }
+          const __half2 ss = __half2half2(__hmul_rn(__int2half_rn(sc), d));
+          const __half2 sm = __half2half2(__hmul_rn(__int2half_rn(mn), dmin));
+#pragma unroll
+          for (int i = 0; i < 4; i++) o[4 * sb + i] = dequant8<T>(w8[4 * sb + i], ss, sm);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) o[i] = make_uint4(0, 0, 0, 0);
+      }
+      // 16-byte chunk c of row p sits at chunk position c ^ (p & 7) (128-byte swizzle)
+#pragma unroll
+      for (int c = 0; c < 8; c++) *reinterpret_cast<uint4*>(brow + ((c ^ (p & 7)) << 4)) = o[c];
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sh->full_b[s]));
+    }
+    // ===== epilogue: warp (warp % 4) owns TMEM lanes 32 * (warp % 4) ..; the two sets of four
+    // producer warps split the column chunks between them =====
+    if (__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->acc_full), 0, dead))) {   // warp-uniform: tcgen05.ld is .aligned
+      tc_fence_after();
+      const int quarter = warp & 3, half = (warp - 2) >> 2;
+      T* yb = reinterpret_cast<T*>(P.y);
+      const T* bias = reinterpret_cast<const T*>(P.bias);
+#pragma unroll 1
+      for (int a = 0; a < MT; a++) {
+        const int m = m0 + a * kBM + quarter * 32 + lane;
+#pragma unroll 1
+        for (int ch = half; ch < kBN / 32; ch += 2) {
+          uint32_t r[32];
+          tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * kBN + ch * 32), r);
+          const int nc = n0 + ch * 32;
+          if (m < P.M) {
+            T* dst = yb + (size_t)m * P.N + nc;
+            if (nc + 32 <= P.N && (P.N & 7) == 0) {
+#pragma unroll
+              for (int v4 = 0; v4 < 4; v4++) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                  float f0 = __uint_as_float(r[8 * v4 + 2 * e]), f1 = __uint_as_float(r[8 * v4 + 2 * e + 1]);
+                  if (bias) { f0 += Act<T>::to_f(bias[nc + 8 * v4 + 2 * e]); f1 += Act<T>::to_f(bias[nc + 8 * v4 + 2 * e + 1]); }
+                  const T t0 = Act<T>::from_f(f0), t1 = Act<T>::from_f(f1);
+                  pk[e] = (uint32_t)(*reinterpret_cast<const unsigned short*>(&t0)) |
+                          ((uint32_t)(*reinterpret_cast<const unsigned short*>(&t1)) << 16);
+                }
+                *reinterpret_cast<uint4*>(dst + 8 * v4) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              }
+            } else {
+              for (int e = 0; e < 32; e++) {
+                if (nc + e < P.N) {
+                  float f = __uint_as_float(r[e]);
+                  if (bias) f += Act<T>::to_f(bias[nc + e]);
+                  dst[e] = Act<T>::from_f(f);
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, kCols);
+  }
+  if (tid == 0 && sh->dead) atomicExch(P.status, MLXR_ERR_TIMEOUT);
+}
+
+}  // namespace prefill
+
+// ---- host side -----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// X [M, K] of a 16-bit type as a 2-D tensor (K inner), boxes of 64 x 128 elements with the
+// 128-byte swizzle; rows past M read as zero.
+static int x_tensor_map(const void* x, int M, int K, int dtype, CUtensorMap* out) {
+  static EncodeTiledFn encode = nullptr;
+  static std::mutex mu;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (!encode) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      MLXR_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+      if (!fn || q != cudaDriverEntryPointSuccess) { set_error("cuTensorMapEncodeTiled is not available in this driver"); return MLXR_ERR_CUDA; }
+      encode = (EncodeTiledFn)fn;
+    }
+  }
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)prefill::kBK, (cuuint32_t)prefill::kBM};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(out, dtype == MLXR_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                            const_cast<void*>(x), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%d) for X [%d, %d]", (int)r, M, K); return MLXR_ERR_CUDA; }
+  return MLXR_OK;
+}
+
+bool prefill_supported(int qt, int M, int N, int K, int dtype, const void* x, const void* w, const void* y) {
+  if (qt != MLXR_Q4_K || (dtype != MLXR_F16 && dtype != MLXR_BF16)) return false;
+  if (M < 9 || N < 1 || K < 256 || K % 256 != 0) return false;
+  if ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)y)) & 15u) return false;
+  return true;
+}
+
+template <typename T, int MT, int STAGES>
+static int launch_tc(const CUtensorMap& xmap, const prefill::Params& P, cudaStream_t st) {
+  using namespace prefill;
+  auto kern = qgemm_tc_kernel<T, MT, STAGES>;
+  constexpr size_t smem = (size_t)STAGES * (MT * kATile + kBTile) + sizeof(Shared) + 1024;
+  static bool attr_done[64] = {};
+  int dev = 0;
+  MLXR_CUDA_TRY(cudaGetDevice(&dev));
+  if (!attr_done[dev & 63]) {
+    MLXR_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_done[dev & 63] = true;
+  }
+  dim3 grid((P.N + kBN - 1) / kBN, (P.M + MT * kBM - 1) / (MT * kBM));
+  kern<<<grid, kThreads, smem, st>>>(xmap, P);
+  MLXR_LAUNCH_CHECK("qgemm_tc_kernel");
+  return MLXR_OK;
+}
+
+int launch_prefill(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int qt, int dtype,
+                   int* status, cudaStream_t st) {
+  (void)qt;
+  CUtensorMap xmap;
+  if (int r = x_tensor_map(x, M, K, dtype, &xmap)) return r;
+  prefill::Params P;
+  P.w = (const uint8_t*)w;
+  P.bias = bias;
+  P.y = y;
+  P.M = M; P.N = N; P.K = K;
+  P.row_bytes = (size_t)(K / 256) * 144;
+  P.status = status;
+  const bool two = M > prefill::kBM;      // a second accumulator only pays when there are rows for it
+  if (dtype == MLXR_F16) return two ? launch_tc<__half, 2, 3>(xmap, P, st) : launch_tc<__half, 1, 4>(xmap, P, st);
+  return two ? launch_tc<__nv_bfloat16, 2, 3>(xmap, P, st) : launch_tc<__nv_bfloat16, 1, 4>(xmap, P, st);
+}
+
+}  // namespace mlxr
