@@ -200,6 +200,27 @@ MLXR_API int mlxr_mlp_block_dense(const void* x, const void* w_gate, const void*
  * call).  The return value is the status of this call itself. */
 MLXR_API int mlxr_stream_status(void* stream, int* status_out);
 
+/* The decode linear (1 <= M <= 8, Q4_K or Q4_0, K a multiple of 256) with NO device allocation,
+ * on the first call or later: the kernel's scratch (split-K partial sums, barrier and counter
+ * words, status word) is a fixed 4 MiB array inside the loaded module instead of the
+ * per-stream workspace that the other entry points cudaMalloc on first use.  No counterpart
+ * in the reference (Metal buffers come from MLX's allocator); it exists for hosts that must
+ * not allocate at call time - all device memory already given to their own pool, or a path
+ * where an allocation's device-wide synchronisation is not acceptable.
+ *   - N <= MLXR_STATIC_MAX_N, otherwise MLXR_ERR_WORKSPACE (nothing is truncated); shapes
+ *     outside the decode range give MLXR_ERR_UNSUPPORTED.
+ *   - The array exists once per device: calls that overlap in time on one device (different
+ *     streams) race on it.  Order them (one stream, or events).
+ *   - The first call on a device fetches the array's address, zeroes the words that must
+ *     start at zero and sets kernel attributes: make it before any stream capture begins.
+ *   - A bounded wait that gives up is recorded in the array's own status word, which
+ *     mlxr_stream_status does not read.
+ * Same arithmetic and the same results as mlxr_q_gemm_dequant for these shapes. */
+#define MLXR_STATIC_MAX_N 8192
+MLXR_API int mlxr_q_gemm_dequant_static(const void* x, const void* weights, const void* bias,
+                                        void* y, int M, int N, int K, int quant_type, int dtype,
+                                        void* stream);
+
 /* How the persistent decode kernel is launched (process-wide; no counterpart in the
  * reference, whose Metal command buffers serialise kernels).
  *   MLXR_DECODE_LAUNCH_OVERLAPPED (default): plain launch with programmatic stream

@@ -46,6 +46,7 @@ PROTOTYPES = {
     "mlxr_stream_status": (_i, [_vp, _vp]),
     "mlxr_debug_set_trace_buffer": (_i, [_vp]),
     "mlxr_set_decode_launch_mode": (_i, [_i]),
+    "mlxr_q_gemm_dequant_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "mlxr_qkv_rope": (_i, [_vp] * 11 + [_i] * 7 + [_f, _i, _i, _vp]),
     "mlxr_q_gemm_dequant_host": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "mlxr_mlp_block_host": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp]),
