@@ -352,6 +352,86 @@ def run_mine(args):
         dist.destroy_process_group()
 
 
+def run_prefill(args):
+    """Prefill Q-GEMM: Y[M, N] = X[M, K] * dequant(W[N, K])^T, Q4_K weights, bf16 activations,
+    one linear of the Llama-3-8B MLP (N = inter, K = hidden by default; --transpose for the
+    down projection).  value = TFLOP/s (2 M N K per step); the bound is the tensor pipe."""
+    import torch
+
+    import mlxr_b200 as mx
+    from mlxr_b200._capi import check, lib
+
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    if int(os.environ.get("RANK", "0")) != 0:
+        return                      # a single linear has no exchange step: replicas only
+    M = args.batch
+    N, K = (SIZES["hidden"], SIZES["inter"]) if args.transpose else (SIZES["inter"], SIZES["hidden"])
+    steps, W = args.steps, max(args.warmup, 3)
+    from mlxr_b200.quantize import quantize
+    g = lambda i: np.random.Generator(np.random.PCG64(SEED + i))
+    w = torch.from_numpy(quantize((g(1).standard_normal((N, K)) * 0.02).astype(np.float32), QT_Q4_K)).cuda()
+    copies = max(2, int(np.ceil(300e6 / (M * K * 2))))          # rotate X so that it does not sit in L2
+    xs = [torch.from_numpy(g(10 + i).standard_normal((M, K)).astype(np.float32)).bfloat16().cuda() for i in range(min(copies, 8))]
+    y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+
+    def step(i):
+        check(lib.mlxr_q_gemm_dequant(xs[i % len(xs)].data_ptr(), w.data_ptr(), None, y.data_ptr(), M, N, K, QT_Q4_K, 256, 1, st))
+
+    for i in range(W):
+        step(i)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    l0 = lib.mlxr_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for i in range(steps):
+        step(W + i)
+    e1.record()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    launches = lib.mlxr_launch_count() - l0
+    clocks = sampler.stop(t0, t1)
+    ms_step = e0.elapsed_time(e1) / steps
+    status = ctypes.c_int(0)
+    check(lib.mlxr_stream_status(st, ctypes.byref(status)))
+    assert status.value == 0 and torch.isfinite(y.float()).all()
+
+    xh = xs[0].cpu().pin_memory()
+    yh = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+    ke = max(3, min(steps, 20))
+    for i in range(2):
+        check(lib.mlxr_q_gemm_dequant_host(xh.data_ptr(), w.data_ptr(), None, yh.data_ptr(), M, N, K, QT_Q4_K, 256, 1, st))
+    torch.cuda.synchronize()
+    th0 = time.perf_counter()
+    for i in range(ke):
+        check(lib.mlxr_q_gemm_dequant_host(xh.data_ptr(), w.data_ptr(), None, yh.data_ptr(), M, N, K, QT_Q4_K, 256, 1, st))
+    torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - th0) / ke
+
+    _, tf, which = measured_peaks()
+    flops = 2.0 * M * N * K
+    achieved = flops / (ms_step * 1e-3) / 1e12
+    line = {
+        "metric": "prefill_qgemm_tflops", "value": achieved, "unit": "TFLOP/s", "n_gpus": 1, "steps": steps, "warmup": W,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": f"prefill Q-GEMM [{M}, {K}] x Q4_K [{N}, {K}]^T, bf16 activations, fp32 accumulation "
+                               f"(tcgen05 / TMEM)", "batch": M, "quant": "Q4_K (MLXR layout)", "parallelism": "single GPU",
+                   "l2": f"X rotates over {len(xs)} device copies; W (33 MB packed) is L2-resident by design"},
+        "e2e": {"value": flops / e2e_s / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K * 2, "d2h_bytes_per_step": M * N * 2,
+                "ms_per_step": e2e_s * 1e3},
+        "gpu_launches": int(launches), "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf, "unit": "TFLOP/s", "frac": achieved / tf,
+                     "traffic": None, "peak_source": which + " (burst bf16 figure)", "flops_per_step": flops,
+                     "kernel": "qgemm_tc_kernel", "timing": "CUDA events around K plain launches"},
+        "cpu_baseline": None,
+    }
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -363,12 +443,18 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--hidden", type=int, default=H)
     ap.add_argument("--inter", type=int, default=I)
+    ap.add_argument("--workload", default="mlp_decode", choices=["mlp_decode", "prefill"])
+    ap.add_argument("--transpose", action="store_true", help="prefill: the down-projection shape (N = hidden, K = inter)")
     ap.add_argument("--exchange", default="auto", choices=["auto", "nccl_f32", "nccl_act", "peer"],
                     help="how the ranks' partial sums are added (N > 1)")
     args = ap.parse_args()
     SIZES["hidden"], SIZES["inter"] = args.hidden, args.inter
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "prefill":
+        if args.batch == 1:
+            args.batch = 2048
+        run_prefill(args)
     else:
         run_mine(args)
 

@@ -3,10 +3,11 @@
 //
 // One CTA computes a (MT x 128) x 256 output tile over the whole K:
 //   * X tiles (128 rows x 64 K, 16 KB each) arrive by 2-D tensor TMA with the 128-byte swizzle;
-//   * eight producer warps read the packed Q4_K rows (one weight row per thread), dequantize
-//     with the reference shader's half arithmetic (q_gemm_dequant.metal:214-259; bit-exact
-//     fp16 values), round to the activation dtype and store them as the K-major, 128-byte
-//     swizzled B tile (256 rows x 64 K, 32 KB);
+//   * sixteen producer warps read the packed Q4_K rows (one weight row and 32-weight sub-block
+//     per thread and stage), dequantize (fp16 activations: the reference shader's half
+//     arithmetic, q_gemm_dequant.metal:214-259, bit-exact; bf16 activations: one fp32
+//     multiply-add from the exact fp16 scale and min, rounded once to bf16) and store the
+//     K-major, 128-byte swizzled B tile (256 rows x 64 K, 32 KB);
 //   * one thread issues tcgen05.mma (cta_group::1, 128 x 256 x 16, fp32 accumulators in tensor
 //     memory); the same B tile feeds MT accumulators (MT x 256 columns of TMEM), which halves
 //     the dequantization work per flop at MT = 2;
@@ -33,8 +34,8 @@ constexpr int kBM = 128;          // rows of X per accumulator (MMA M)
 constexpr int kBN = 256;          // weight rows per tile (MMA N)
 constexpr int kBK = 64;           // K per stage: one 128-byte swizzle row of 16-bit elements
 constexpr int kUmmaK = 16;
-constexpr int kProducerWarps = 8; // one weight row per producer thread
-constexpr int kThreads = (2 + kProducerWarps) * 32;
+constexpr int kProducerWarps = 16; // one (weight row, 32-weight sub-block) per producer thread and stage
+constexpr int kThreads = (1 + kProducerWarps) * 32;
 constexpr int kATile = kBM * kBK * 2;     // 16 KB
 constexpr int kBTile = kBN * kBK * 2;     // 32 KB
 constexpr uint32_t kSpin = 1u << 22;
@@ -46,6 +47,7 @@ struct Params {
   int M, N, K;
   size_t row_bytes;
   int* status;
+  int debug;          // tuning probes: 1 skip the conversion math, 2 skip the weight loads
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -138,23 +140,12 @@ template <typename T> struct Fmt;
 template <> struct Fmt<__half> { static constexpr int v = 0; };
 template <> struct Fmt<__nv_bfloat16> { static constexpr int v = 1; };
 
-// two reference-exact fp16 weights -> one 32-bit pair of the activation dtype
-template <typename T>
-__device__ __forceinline__ uint32_t pack_pair(__half2 v) {
-  if constexpr (sizeof(T) == 2 && Fmt<T>::v == 0) {
-    return *reinterpret_cast<uint32_t*>(&v);
-  } else {
-    const float2 f = __half22float2(v);
-    __nv_bfloat162 b = __float22bfloat162_rn(f);
-    return *reinterpret_cast<uint32_t*>(&b);
-  }
-}
-
 // Eight consecutive weights of a Q4_K sub-block (one 32-bit word of nibbles, element order =
-// nibble order) -> four packed pairs.  1024 + n as fp16 is 0x6400 | n; subtracting 1032 gives
-// n - 8 exactly; then the shader's two roundings: rn16(rn16((n - 8) * ss) + sm).
-template <typename T>
-__device__ __forceinline__ uint4 dequant8(uint32_t v, __half2 ss, __half2 sm) {
+// nibble order) -> four packed pairs of the activation dtype.
+//
+// fp16 activations: the shader's arithmetic exactly (q_gemm_dequant.metal:244-256).  1024 + n as
+// fp16 is 0x6400 | n; subtracting 1032 gives n - 8 exactly; then rn16(rn16((n - 8) * ss) + sm).
+__device__ __forceinline__ uint4 dequant8_f16(uint32_t v, __half2 ss, __half2 sm) {
   const uint32_t lo = v & 0x0F0F0F0Fu, hi = (v >> 4) & 0x0F0F0F0Fu;
   const __half2 off = __half2half2(__ushort_as_half((unsigned short)0x6408));   // 1032
   uint32_t out[4];
@@ -164,7 +155,24 @@ __device__ __forceinline__ uint4 dequant8(uint32_t v, __half2 ss, __half2 sm) {
     uint32_t bits = (__byte_perm(lo, hi, sel) & 0x00FF00FFu) | 0x64006400u;
     const __half2 q = __hsub2(*reinterpret_cast<__half2*>(&bits), off);
     const __half2 r = __hadd2_rn(__hmul2_rn(q, ss), sm);
-    out[j] = pack_pair<T>(r);
+    out[j] = *reinterpret_cast<const uint32_t*>(&r);
+  }
+  return make_uint4(out[0], out[1], out[2], out[3]);
+}
+// bf16 activations: the weight is rounded to bf16 for the MMA anyway (2^-9 relative), so the two
+// fp16 roundings of the shader are not reproduced; one fp32 multiply-add per weight from the
+// exact fp16 scale and min, then one rounding to bf16.  The nibble becomes the fp32 number
+// 128 + n by a byte permute (bits 0x4300'0000 | n << 16), so w = (128 + n) * ss + (sm - 136 ss).
+__device__ __forceinline__ uint4 dequant8_bf16(uint32_t v, float ss, float c) {
+  const uint32_t lo = v & 0x0F0F0F0Fu, hi = (v >> 4) & 0x0F0F0F0Fu;
+  uint32_t out[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    // result bytes (0, 0, nibble, 0x43): sources 6/7 are the zero bytes of 0x00004300, 5 is 0x43
+    const float fe = __uint_as_float(__byte_perm(lo, 0x00004300u, 0x5066u | ((uint32_t)j << 8)));
+    const float fo = __uint_as_float(__byte_perm(hi, 0x00004300u, 0x5066u | ((uint32_t)j << 8)));
+    __nv_bfloat162 b = __floats2bfloat162_rn(fmaf(fe, ss, c), fmaf(fo, ss, c));
+    out[j] = *reinterpret_cast<const uint32_t*>(&b);
   }
   return make_uint4(out[0], out[1], out[2], out[3]);
 }
@@ -179,6 +187,9 @@ struct Shared {
 };
 
 // MT accumulators (MT x 128 rows of X) per CTA, STAGES pipeline stages.
+// Warp 0: tensor-memory owner and MMA issuer (lane 0).  Warps 1..16: producers; thread pp of them
+// owns (weight row pp & 255, sub-block pp >> 8 of the 64-wide k-block); the first of them also
+// issues the TMA copies of the X tiles, since it waits for the stage to be free anyway.
 template <typename T, int MT, int STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
@@ -206,35 +217,13 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(smem_u32(&sh->tmem_base), kCols);
+  if (warp == 0) tmem_alloc(smem_u32(&sh->tmem_base), kCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&sh->tmem_base);
 
   if (warp == 0) {
-    // ===== TMA producer of the X tiles =====
-    if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < nkb; kb++) {
-        const int s = kb % STAGES, it = kb / STAGES;
-        if (!mbar_wait(smem_u32(&sh->empty[s]), (it & 1) ^ 1, dead)) break;
-        const uint32_t bar = smem_u32(&sh->full_a[s]);
-        mbar_expect_tx(bar, MT * kATile);
-#pragma unroll
-        for (int a = 0; a < MT; a++)
-          tma_load_2d(smem_u32(smem + (size_t)s * kStageBytes + a * kATile), &xmap, kb * kBK, m0 + a * kBM, bar);
-        issued = kb + 1;
-      }
-      if (*dead) {
-        // copies in flight must land before the CTA may exit (bounded)
-        for (int kb = max(0, issued - STAGES); kb < issued; kb++) {
-          const uint32_t bar = smem_u32(&sh->full_a[kb % STAGES]);
-          for (uint32_t i = 0; i < kSpin; i++) if (mbar_try(bar, (kb / STAGES) & 1)) break;
-        }
-      }
-    }
-  } else if (warp == 1) {
     // ===== MMA issuer =====
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(Fmt<T>::v, kBM, kBN);
@@ -260,101 +249,127 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
       if (ok) umma_commit(smem_u32(&sh->acc_full));
     }
   } else {
-    // ===== dequantizing producers: thread p owns weight row n0 + p =====
-    const int p = tid - 64;
+    // ===== dequantizing producers =====
+    const int pp = tid - 32;
+    const int p = pp & (kBN - 1), hb = pp >> 8;          // weight row of the tile, sub-block of the k-block
     const int n = n0 + p;
     const bool live = n < P.N;
     const uint8_t* rowp = P.w + (size_t)(live ? n : 0) * P.row_bytes;
+    const bool tma_thread = (pp == 0);
     uint4 q0 = make_uint4(0, 0, 0, 0), q1 = q0, hdr = q0;
-    auto fetch = [&](int kb) {
-      // k-block kb: super-block kb / 4, sub-blocks 2 * (kb % 4) and the next one
+    // k-block kb: super-block kb / 4, this thread's sub-block s = 2 * (kb % 4) + hb (16 bytes of nibbles)
+    auto fetch = [&](int kb, uint4& q) {
       const uint8_t* blk = rowp + (size_t)(kb >> 2) * 144;
       if ((kb & 3) == 0) hdr = __ldg(reinterpret_cast<const uint4*>(blk));
-      q0 = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * (kb & 3)));
-      q1 = __ldg(reinterpret_cast<const uint4*>(blk + 32 + 32 * (kb & 3)));
+      q = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * (kb & 3) + 16 * hb));
     };
-    if (live) fetch(0);
+    // nibbles are requested two k-blocks ahead (q0: even, q1: odd k-blocks); the header of a
+    // super-block arrives with its first k-block and is copied out before the next one overwrites it
+    const bool loads = live && !(P.debug & 2);
+    uint4 ch = make_uint4(0, 0, 0, 0);
+    if (loads) { fetch(0, q0); ch = hdr; if (nkb > 1) fetch(1, q1); }
+    int issued = 0;
     for (int kb = 0; kb < nkb; kb++) {
       const int s = kb % STAGES, it = kb / STAGES;
-      const uint4 c0 = q0, c1 = q1, ch = hdr;
-      if (live && kb + 1 < nkb) fetch(kb + 1);
+      const uint4 cq = (kb & 1) ? q1 : q0;
+      if ((kb & 3) == 0) ch = hdr;
+      if (loads && kb + 2 < nkb) { if (kb & 1) fetch(kb + 2, q1); else fetch(kb + 2, q0); }
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->empty[s]), (it & 1) ^ 1, dead))) break;   // warp-uniform
+      if (tma_thread) {
+        const uint32_t bar = smem_u32(&sh->full_a[s]);
+        mbar_expect_tx(bar, MT * kATile);
+#pragma unroll
+        for (int a = 0; a < MT; a++)
+          tma_load_2d(smem_u32(smem + (size_t)s * kStageBytes + a * kATile), &xmap, kb * kBK, m0 + a * kBM, bar);
+        issued = kb + 1;
+      }
       uint8_t* brow = smem + (size_t)s * kStageBytes + MT * kATile + (size_t)p * 128;
-      uint4 o[8];
-      if (live) {
-        // header: d, dmin (fp16), scales[12] -> (scale, min) of the two sub-blocks
+      uint4 o[4];
+      if (live && (P.debug & 1)) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) o[i] = cq;
+      } else if (live) {
+        // header: d, dmin (fp16), scales[12].  scales[3g .. 3g+2] of group g = (kb & 3) >> 1 as
+        // one 24-bit value (only scales[0..5] are read); sub-block offset o = (2 (kb & 3) + hb) & 3:
+        // only o == 1 takes the second pair (offsets 2 and 3 alias offset 0, q_gemm_dequant.metal:222-242)
         const __half d = __ushort_as_half((unsigned short)(ch.x & 0xFFFFu));
         const __half dmin = __ushort_as_half((unsigned short)(ch.x >> 16));
-        // scales[3g .. 3g+2] of group g = (kb & 3) >> 1 as one 24-bit value (only scales[0..5] are read)
         const uint32_t t24 = (kb & 2) ? ((ch.y >> 24) | ((ch.z & 0xFFFFu) << 8)) : (ch.y & 0xFFFFFFu);
-        const uint32_t w8[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const uint32_t b0 = t24 & 0xFFu, b1 = (t24 >> 8) & 0xFFu, b2 = (t24 >> 16) & 0xFFu;
+        int sc, mn;
+        if (((kb & 1) == 0) && hb == 1) {
+          sc = (int)(((b1 >> 4) | ((b2 & 0x03u) << 4)) & 0x3Fu);
+          mn = (int)((b2 >> 2) & 0x3Fu);
+        } else {
+          sc = (int)(b0 & 0x3Fu);
+          mn = (int)(((b0 >> 6) | ((b1 & 0x0Fu) << 2)) & 0x3Fu);
+        }
+        const __half ssh = __hmul_rn(__int2half_rn(sc), d), smh = __hmul_rn(__int2half_rn(mn), dmin);
+        const uint32_t w4[4] = {cq.x, cq.y, cq.z, cq.w};
+        if constexpr (Fmt<T>::v == 0) {
+          const __half2 ss = __half2half2(ssh), sm = __half2half2(smh);
 #pragma unroll
-        for (int sb = 0; sb < 2; sb++) {
-          // sub-block offset o = (2 * (kb & 3) + sb) & 3: only o == 1 takes the second pair
-          // (offsets 2 and 3 alias offset 0, q_gemm_dequant.metal:222-242)
-          int sc, mn;
-          const uint32_t b0 = t24 & 0xFFu, b1 = (t24 >> 8) & 0xFFu, b2 = (t24 >> 16) & 0xFFu;
-          if (((kb & 1) == 0) && sb == 1) {
-            sc = (int)(((b1 >> 4) | ((b2 & 0x03u) << 4)) & 0x3Fu);
-            mn = (int)((b2 >> 2) & 0x3Fu);
-          } else {
-            sc = (int)(b0 & 0x3Fu);
-            mn = (int)(((b0 >> 6) | ((b1 & 0x0Fu) << 2)) & 0x3Fu);
-          }
-          const __half2 ss = __half2half2(__hmul_rn(__int2half_rn(sc), d));
-          const __half2 sm = __half2half2(__hmul_rn(__int2half_rn(mn), dmin));
+          for (int i = 0; i < 4; i++) o[i] = dequant8_f16(w4[i], ss, sm);
+        } else {
+          const float ss = __half2float(ssh), c = fmaf(-136.0f, ss, __half2float(smh));
 #pragma unroll
-          for (int i = 0; i < 4; i++) o[4 * sb + i] = dequant8<T>(w8[4 * sb + i], ss, sm);
+          for (int i = 0; i < 4; i++) o[i] = dequant8_bf16(w4[i], ss, c);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 8; i++) o[i] = make_uint4(0, 0, 0, 0);
+        for (int i = 0; i < 4; i++) o[i] = make_uint4(0, 0, 0, 0);
       }
       // 16-byte chunk c of row p sits at chunk position c ^ (p & 7) (128-byte swizzle)
 #pragma unroll
-      for (int c = 0; c < 8; c++) *reinterpret_cast<uint4*>(brow + ((c ^ (p & 7)) << 4)) = o[c];
+      for (int i = 0; i < 4; i++) *reinterpret_cast<uint4*>(brow + (((4 * hb + i) ^ (p & 7)) << 4)) = o[i];
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sh->full_b[s]));
     }
-    // ===== epilogue: warp (warp % 4) owns TMEM lanes 32 * (warp % 4) ..; the two sets of four
-    // producer warps split the column chunks between them =====
+    if (tma_thread && *dead) {
+      // copies in flight must land before the CTA may exit (bounded)
+      for (int kb = max(0, issued - STAGES); kb < issued; kb++) {
+        const uint32_t bar = smem_u32(&sh->full_a[kb % STAGES]);
+        for (uint32_t i = 0; i < kSpin; i++) if (mbar_try(bar, (kb / STAGES) & 1)) break;
+      }
+    }
+    __syncwarp();
+    // ===== epilogue: warp (warp % 4) owns TMEM lanes 32 * (warp % 4) ..; the four producer
+    // warps of a quarter share the (accumulator, 32-column chunk) units between them =====
     if (__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->acc_full), 0, dead))) {   // warp-uniform: tcgen05.ld is .aligned
       tc_fence_after();
-      const int quarter = warp & 3, half = (warp - 2) >> 2;
+      const int quarter = warp & 3, gi = (warp - 1) >> 2;
       T* yb = reinterpret_cast<T*>(P.y);
       const T* bias = reinterpret_cast<const T*>(P.bias);
 #pragma unroll 1
-      for (int a = 0; a < MT; a++) {
+      for (int u = gi; u < MT * (kBN / 32); u += 4) {
+        const int a = u / (kBN / 32), chn = u % (kBN / 32);
         const int m = m0 + a * kBM + quarter * 32 + lane;
-#pragma unroll 1
-        for (int ch = half; ch < kBN / 32; ch += 2) {
-          uint32_t r[32];
-          tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * kBN + ch * 32), r);
-          const int nc = n0 + ch * 32;
-          if (m < P.M) {
-            T* dst = yb + (size_t)m * P.N + nc;
-            if (nc + 32 <= P.N && (P.N & 7) == 0) {
+        uint32_t r[32];
+        tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * kBN + chn * 32), r);
+        const int nc = n0 + chn * 32;
+        if (m < P.M) {
+          T* dst = yb + (size_t)m * P.N + nc;
+          if (nc + 32 <= P.N && (P.N & 7) == 0) {
 #pragma unroll
-              for (int v4 = 0; v4 < 4; v4++) {
-                uint32_t pk[4];
+            for (int v4 = 0; v4 < 4; v4++) {
+              uint32_t pk[4];
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                  float f0 = __uint_as_float(r[8 * v4 + 2 * e]), f1 = __uint_as_float(r[8 * v4 + 2 * e + 1]);
-                  if (bias) { f0 += Act<T>::to_f(bias[nc + 8 * v4 + 2 * e]); f1 += Act<T>::to_f(bias[nc + 8 * v4 + 2 * e + 1]); }
-                  const T t0 = Act<T>::from_f(f0), t1 = Act<T>::from_f(f1);
-                  pk[e] = (uint32_t)(*reinterpret_cast<const unsigned short*>(&t0)) |
-                          ((uint32_t)(*reinterpret_cast<const unsigned short*>(&t1)) << 16);
-                }
-                *reinterpret_cast<uint4*>(dst + 8 * v4) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+              for (int e = 0; e < 4; e++) {
+                float f0 = __uint_as_float(r[8 * v4 + 2 * e]), f1 = __uint_as_float(r[8 * v4 + 2 * e + 1]);
+                if (bias) { f0 += Act<T>::to_f(bias[nc + 8 * v4 + 2 * e]); f1 += Act<T>::to_f(bias[nc + 8 * v4 + 2 * e + 1]); }
+                const T t0 = Act<T>::from_f(f0), t1 = Act<T>::from_f(f1);
+                pk[e] = (uint32_t)(*reinterpret_cast<const unsigned short*>(&t0)) |
+                        ((uint32_t)(*reinterpret_cast<const unsigned short*>(&t1)) << 16);
               }
-            } else {
-              for (int e = 0; e < 32; e++) {
-                if (nc + e < P.N) {
-                  float f = __uint_as_float(r[e]);
-                  if (bias) f += Act<T>::to_f(bias[nc + e]);
-                  dst[e] = Act<T>::from_f(f);
-                }
+              *reinterpret_cast<uint4*>(dst + 8 * v4) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+          } else {
+            for (int e = 0; e < 32; e++) {
+              if (nc + e < P.N) {
+                float f = __uint_as_float(r[e]);
+                if (bias) f += Act<T>::to_f(bias[nc + e]);
+                dst[e] = Act<T>::from_f(f);
               }
             }
           }
@@ -364,7 +379,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 0) {
     tc_fence_after();
     tmem_dealloc(tmem, kCols);
   }
@@ -441,6 +456,8 @@ int launch_prefill(const void* x, const void* w, const void* bias, void* y, int 
   P.M = M; P.N = N; P.K = K;
   P.row_bytes = (size_t)(K / 256) * 144;
   P.status = status;
+  P.debug = 0;
+  if (const char* e = getenv("MLXR_TC_DEBUG")) P.debug = atoi(e);   // tuning probe
   const bool two = M > prefill::kBM;      // a second accumulator only pays when there are rows for it
   if (dtype == MLXR_F16) return two ? launch_tc<__half, 2, 3>(xmap, P, st) : launch_tc<__half, 1, 4>(xmap, P, st);
   return two ? launch_tc<__nv_bfloat16, 2, 3>(xmap, P, st) : launch_tc<__nv_bfloat16, 1, 4>(xmap, P, st);
