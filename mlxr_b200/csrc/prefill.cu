@@ -132,8 +132,8 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 }
 // Instruction descriptor of kind::f16: fp32 accumulate, A and B of format `fmt` (0 fp16, 1 bf16),
 // both K-major, N and M of the MMA.
-__host__ __device__ constexpr uint32_t instr_desc(int fmt, int m, int n) {
-  return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+__host__ __device__ constexpr uint32_t instr_desc(int afmt, int bfmt, int m, int n) {
+  return (1u << 4) | ((uint32_t)afmt << 7) | ((uint32_t)bfmt << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 template <typename T> struct Fmt;
@@ -190,7 +190,7 @@ struct Shared {
 // Warp 0: tensor-memory owner and MMA issuer (lane 0).  Warps 1..16: producers; thread pp of them
 // owns (weight row pp & 255, sub-block pp >> 8 of the 64-wide k-block); the first of them also
 // issues the TMA copies of the X tiles, since it waits for the stage to be free anyway.
-template <typename T, int MT, int STAGES>
+template <typename T, int MT, int STAGES, int BF>
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
   extern __shared__ uint8_t smem_raw[];
@@ -226,7 +226,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
   if (warp == 0) {
     // ===== MMA issuer =====
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc(Fmt<T>::v, kBM, kBN);
+      constexpr uint32_t idesc = instr_desc(Fmt<T>::v, BF, kBM, kBN);
       bool ok = true;
       for (int kb = 0; kb < nkb && ok; kb++) {
         const int s = kb % STAGES, it = kb / STAGES;
@@ -306,7 +306,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         }
         const __half ssh = __hmul_rn(__int2half_rn(sc), d), smh = __hmul_rn(__int2half_rn(mn), dmin);
         const uint32_t w4[4] = {cq.x, cq.y, cq.z, cq.w};
-        if constexpr (Fmt<T>::v == 0) {
+        if constexpr (BF == 0) {
           const __half2 ss = __half2half2(ssh), sm = __half2half2(smh);
 #pragma unroll
           for (int i = 0; i < 4; i++) o[i] = dequant8_f16(w4[i], ss, sm);
@@ -426,10 +426,10 @@ bool prefill_supported(int qt, int M, int N, int K, int dtype, const void* x, co
   return true;
 }
 
-template <typename T, int MT, int STAGES>
+template <typename T, int MT, int STAGES, int BF>
 static int launch_tc(const CUtensorMap& xmap, const prefill::Params& P, cudaStream_t st) {
   using namespace prefill;
-  auto kern = qgemm_tc_kernel<T, MT, STAGES>;
+  auto kern = qgemm_tc_kernel<T, MT, STAGES, BF>;
   constexpr size_t smem = (size_t)STAGES * (MT * kATile + kBTile) + sizeof(Shared) + 1024;
   static bool attr_done[64] = {};
   int dev = 0;
@@ -459,8 +459,10 @@ int launch_prefill(const void* x, const void* w, const void* bias, void* y, int 
   P.debug = 0;
   if (const char* e = getenv("MLXR_TC_DEBUG")) P.debug = atoi(e);   // tuning probe
   const bool two = M > prefill::kBM;      // a second accumulator only pays when there are rows for it
-  if (dtype == MLXR_F16) return two ? launch_tc<__half, 2, 3>(xmap, P, st) : launch_tc<__half, 1, 4>(xmap, P, st);
-  return two ? launch_tc<__nv_bfloat16, 2, 3>(xmap, P, st) : launch_tc<__nv_bfloat16, 1, 4>(xmap, P, st);
+  if (dtype == MLXR_F16) return two ? launch_tc<__half, 2, 3, 0>(xmap, P, st) : launch_tc<__half, 1, 4, 0>(xmap, P, st);
+  // kind::f16 needs A and B in one format: a bf16 x fp16 mix raised a CUDA error at launch, so
+  // for bf16 activations the weights are rounded to bf16 as well
+  return two ? launch_tc<__nv_bfloat16, 2, 3, 1>(xmap, P, st) : launch_tc<__nv_bfloat16, 1, 4, 1>(xmap, P, st);
 }
 
 }  // namespace mlxr
