@@ -140,7 +140,8 @@ int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype
   P.nphases = nphases;
   P.M = M;
   P.gridbar = sync;
-  P.bar_base = *bar_host;
+  P.flags = 0;
+  if (const char* e = getenv("MLXR_DEC_FLAGS")) P.flags = (uint32_t)atoi(e);   // tuning override
   P.status = status;
   P.trace = g_trace;
   // batch <= 2 with Q4_K: pairs in the MMA columns, one n-tile per batch row
