@@ -177,6 +177,70 @@ __device__ __forceinline__ uint4 dequant8_bf16(uint32_t v, float ss, float c) {
   return make_uint4(out[0], out[1], out[2], out[3]);
 }
 
+// 32 weights (group hb of k-block kb) of a Q4_0 / Q8_0 / NF4 row -> four 16-byte chunks of the
+// activation dtype.  Blocks of these formats are only 2-byte aligned.  fp16 activations get the
+// reference's value rounded to fp16 (rn16 of the exact product); bf16 one rounding to bf16.
+template <int QT, int BF>
+__device__ __forceinline__ void dequant32_other(const uint8_t* rowp, int kb, int hb, const float* nf4, uint4 (&o)[4]) {
+  if constexpr (QT == MLXR_Q4_0) {
+    const uint8_t* blk = rowp + (size_t)(2 * kb + hb) * 18;          // q_gemm_dequant.metal:142-161
+    const __half d = h_from_bits(ld_u16(blk));
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const uint32_t v = (uint32_t)ld_u16(blk + 2 + 4 * i) | ((uint32_t)ld_u16(blk + 4 + 4 * i) << 16);
+      if constexpr (BF == 0) o[i] = dequant8_f16(v, __half2half2(d), __half2half2(__ushort_as_half((unsigned short)0)));
+      else { const float ss = __half2float(d); o[i] = dequant8_bf16(v, ss, -136.0f * ss); }
+    }
+  } else if constexpr (QT == MLXR_Q8_0) {
+    const uint8_t* blk = rowp + (size_t)(2 * kb + hb) * 34;          // q_gemm_dequant.metal:190-201
+    const __half d = h_from_bits(ld_u16(blk));
+    const float df = __half2float(d);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      uint32_t out[4];
+#pragma unroll
+      for (int h2 = 0; h2 < 2; h2++) {
+        const int wi = 2 * i + h2;
+        const uint32_t u = ((uint32_t)ld_u16(blk + 2 + 4 * wi) | ((uint32_t)ld_u16(blk + 4 + 4 * wi) << 16)) ^ 0x80808080u;  // bytes q + 128
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+          if constexpr (BF == 0) {
+            // 1024 + (q + 128) as fp16 is 0x6400 | byte; minus 1152 gives q exactly; then one rounding of q * d
+            const uint32_t sel = (uint32_t)(2 * j) | ((uint32_t)(2 * j) << 4) | ((uint32_t)(2 * j + 1) << 8) | ((uint32_t)(2 * j + 1) << 12);
+            uint32_t bits = (__byte_perm(u, u, sel) & 0x00FF00FFu) | 0x64006400u;
+            const __half2 q = __hsub2(*reinterpret_cast<__half2*>(&bits), __half2half2(__ushort_as_half((unsigned short)0x6480)));
+            const __half2 r = __hmul2_rn(q, __half2half2(d));
+            out[2 * h2 + j] = *reinterpret_cast<const uint32_t*>(&r);
+          } else {
+            // byte b placed one byte up in 0x4300'0000 is the fp32 number 128 + b / 256
+            const float fe = __uint_as_float(__byte_perm(u, 0x00004300u, 0x5606u | ((uint32_t)(2 * j) << 4)));
+            const float fo = __uint_as_float(__byte_perm(u, 0x00004300u, 0x5606u | ((uint32_t)(2 * j + 1) << 4)));
+            const float s256 = 256.0f * df, c = -32896.0f * df;      // (128 + b/256) * 256 d - (32768 + 128) d = (b - 128) d
+            __nv_bfloat162 b2 = __floats2bfloat162_rn(fmaf(fe, s256, c), fmaf(fo, s256, c));
+            out[2 * h2 + j] = *reinterpret_cast<const uint32_t*>(&b2);
+          }
+        }
+      }
+      o[i] = make_uint4(out[0], out[1], out[2], out[3]);
+    }
+  } else {   // NF4: 64-element blocks of 34 bytes (fp16 absmax, 32 index bytes, low nibble = even element)
+    const uint8_t* blk = rowp + (size_t)kb * 34;
+    const float am = __half2float(h_from_bits(ld_u16(blk)));
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const uint32_t v = (uint32_t)ld_u16(blk + 2 + 16 * hb + 4 * i) | ((uint32_t)ld_u16(blk + 4 + 16 * hb + 4 * i) << 16);
+      uint32_t out[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float fe = nf4[(v >> (8 * j)) & 15u] * am, fo = nf4[(v >> (8 * j + 4)) & 15u] * am;
+        if constexpr (BF == 0) { const __half2 r = __floats2half2_rn(fe, fo); out[j] = *reinterpret_cast<const uint32_t*>(&r); }
+        else { __nv_bfloat162 r = __floats2bfloat162_rn(fe, fo); out[j] = *reinterpret_cast<const uint32_t*>(&r); }
+      }
+      o[i] = make_uint4(out[0], out[1], out[2], out[3]);
+    }
+  }
+}
+
 struct Shared {
   uint64_t full_a[4];
   uint64_t full_b[4];
@@ -184,13 +248,14 @@ struct Shared {
   uint64_t acc_full;
   uint32_t tmem_base;
   int dead;
+  float nf4[16];
 };
 
 // MT accumulators (MT x 128 rows of X) per CTA, STAGES pipeline stages.
 // Warp 0: tensor-memory owner and MMA issuer (lane 0).  Warps 1..16: producers; thread pp of them
 // owns (weight row pp & 255, sub-block pp >> 8 of the 64-wide k-block); the first of them also
 // issues the TMA copies of the X tiles, since it waits for the stage to be free anyway.
-template <typename T, int MT, int STAGES, int BF>
+template <int QT, typename T, int MT, int STAGES, int BF>
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
   extern __shared__ uint8_t smem_raw[];
@@ -206,6 +271,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
   const int nkb = P.K / kBK;
   constexpr uint32_t kCols = MT * kBN;        // TMEM columns (256 or 512: powers of two)
 
+  if (tid >= 32 && tid < 48) sh->nf4[tid - 32] = kNF4[tid - 32];
   if (tid == 0) {
     sh->dead = 0;
     for (int s = 0; s < STAGES; s++) {
@@ -265,7 +331,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     };
     // nibbles are requested two k-blocks ahead (q0: even, q1: odd k-blocks); the header of a
     // super-block arrives with its first k-block and is copied out before the next one overwrites it
-    const bool loads = live && !(P.debug & 2);
+    const bool loads = live && !(P.debug & 2) && QT == MLXR_Q4_K;
     uint4 ch = make_uint4(0, 0, 0, 0);
     if (loads) { fetch(0, q0); ch = hdr; if (nkb > 1) fetch(1, q1); }
     int issued = 0;
@@ -288,6 +354,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
       if (live && (P.debug & 1)) {
 #pragma unroll
         for (int i = 0; i < 4; i++) o[i] = cq;
+      } else if (live && QT != MLXR_Q4_K) {
+        dequant32_other<QT, BF>(rowp, kb, hb, sh->nf4, o);
       } else if (live) {
         // header: d, dmin (fp16), scales[12].  scales[3g .. 3g+2] of group g = (kb & 3) >> 1 as
         // one 24-bit value (only scales[0..5] are read); sub-block offset o = (2 (kb & 3) + hb) & 3:
@@ -420,16 +488,19 @@ static int x_tensor_map(const void* x, int M, int K, int dtype, CUtensorMap* out
 }
 
 bool prefill_supported(int qt, int M, int N, int K, int dtype, const void* x, const void* w, const void* y) {
-  if (qt != MLXR_Q4_K || (dtype != MLXR_F16 && dtype != MLXR_BF16)) return false;
-  if (M < 9 || N < 1 || K < 256 || K % 256 != 0) return false;
-  if ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)y)) & 15u) return false;
+  if (dtype != MLXR_F16 && dtype != MLXR_BF16) return false;
+  if (qt == MLXR_Q4_K) { if (K % 256 != 0 || (((uintptr_t)w) & 15u)) return false; }
+  else if (qt == MLXR_Q4_0 || qt == MLXR_Q8_0 || qt == MLXR_NF4) { if (K % 64 != 0 || (((uintptr_t)w) & 1u)) return false; }
+  else return false;
+  if (M < 9 || N < 1 || K < 64) return false;
+  if ((((uintptr_t)x) | ((uintptr_t)y)) & 15u) return false;
   return true;
 }
 
-template <typename T, int MT, int STAGES, int BF>
+template <int QT, typename T, int MT, int STAGES, int BF>
 static int launch_tc(const CUtensorMap& xmap, const prefill::Params& P, cudaStream_t st) {
   using namespace prefill;
-  auto kern = qgemm_tc_kernel<T, MT, STAGES, BF>;
+  auto kern = qgemm_tc_kernel<QT, T, MT, STAGES, BF>;
   constexpr size_t smem = (size_t)STAGES * (MT * kATile + kBTile) + sizeof(Shared) + 1024;
   static bool attr_done[64] = {};
   int dev = 0;
@@ -446,7 +517,6 @@ static int launch_tc(const CUtensorMap& xmap, const prefill::Params& P, cudaStre
 
 int launch_prefill(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int qt, int dtype,
                    int* status, cudaStream_t st) {
-  (void)qt;
   CUtensorMap xmap;
   if (int r = x_tensor_map(x, M, K, dtype, &xmap)) return r;
   prefill::Params P;
@@ -454,15 +524,28 @@ int launch_prefill(const void* x, const void* w, const void* bias, void* y, int 
   P.bias = bias;
   P.y = y;
   P.M = M; P.N = N; P.K = K;
-  P.row_bytes = (size_t)(K / 256) * 144;
+  P.row_bytes = (size_t)(K / block_elems(qt)) * block_bytes(qt);
   P.status = status;
   P.debug = 0;
   if (const char* e = getenv("MLXR_TC_DEBUG")) P.debug = atoi(e);   // tuning probe
   const bool two = M > prefill::kBM;      // a second accumulator only pays when there are rows for it
-  if (dtype == MLXR_F16) return two ? launch_tc<__half, 2, 3, 0>(xmap, P, st) : launch_tc<__half, 1, 4, 0>(xmap, P, st);
   // kind::f16 needs A and B in one format: a bf16 x fp16 mix raised a CUDA error at launch, so
   // for bf16 activations the weights are rounded to bf16 as well
-  return two ? launch_tc<__nv_bfloat16, 2, 3, 1>(xmap, P, st) : launch_tc<__nv_bfloat16, 1, 4, 1>(xmap, P, st);
+  int rc = MLXR_ERR_UNSUPPORTED;
+#define MLXR_TC_BY_QT(QTV)                                                                                     \
+  do {                                                                                                         \
+    if (dtype == MLXR_F16) rc = two ? launch_tc<QTV, __half, 2, 3, 0>(xmap, P, st) : launch_tc<QTV, __half, 1, 4, 0>(xmap, P, st); \
+    else rc = two ? launch_tc<QTV, __nv_bfloat16, 2, 3, 1>(xmap, P, st) : launch_tc<QTV, __nv_bfloat16, 1, 4, 1>(xmap, P, st);     \
+  } while (0)
+  switch (qt) {
+    case MLXR_Q4_K: MLXR_TC_BY_QT(MLXR_Q4_K); break;
+    case MLXR_Q4_0: MLXR_TC_BY_QT(MLXR_Q4_0); break;
+    case MLXR_Q8_0: MLXR_TC_BY_QT(MLXR_Q8_0); break;
+    case MLXR_NF4: MLXR_TC_BY_QT(MLXR_NF4); break;
+    default: set_error("tensor-core GEMM: no producer for %s", mlxr_quant_type_name(qt)); break;
+  }
+#undef MLXR_TC_BY_QT
+  return rc;
 }
 
 }  // namespace mlxr

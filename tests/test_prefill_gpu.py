@@ -13,26 +13,26 @@ DT = {"f16": torch.float16, "bf16": torch.bfloat16}
 TIGHT = {"f16": 2e-3, "bf16": 1e-2}
 
 
-def _run(oracle, M, N, K, dt, bias=False, seed=0, rows=None):
+def _run(oracle, M, N, K, dt, bias=False, seed=0, rows=None, qt=3):
     import mlxr_b200 as mx
     from mlxr_b200.quantize import quantize
-    packed = quantize(make_weights(N, K, 100 + seed), 3)
+    packed = quantize(make_weights(N, K, 100 + seed), qt)
     xt, xf = make_acts(M, K, 200 + seed, DT[dt])
     bt = bf = None
     if bias:
         bt, bf = make_acts(1, N, 300 + seed, DT[dt])
         bt, bf = bt[0].contiguous(), bf[0]
-    y = mx.q_gemm_dequant(xt.cuda(), torch.from_numpy(packed).cuda(), M, N, K, mx.QuantType.Q4_K, 256,
-                          bt.cuda() if bias else None)
+    y = mx.q_gemm_dequant(xt.cuda(), torch.from_numpy(packed).cuda(), M, N, K, mx.QuantType(qt),
+                          mx._capi.lib.mlxr_default_group_size(qt), bt.cuda() if bias else None)
     torch.cuda.synchronize()
     st = torch.zeros(1, dtype=torch.int32)
     mx._capi.check(mx._capi.lib.mlxr_stream_status(torch.cuda.current_stream().cuda_stream, st.data_ptr()))
     assert int(st[0]) == 0
     yn = y.float().cpu().numpy()
     if rows is not None:
-        ref = oracle.linear(xf[rows], packed, N, 3, bf)
+        ref = oracle.linear(xf[rows], packed, N, qt, bf)
         return oracle.rel_l2(yn[rows], ref)
-    return oracle.rel_l2(yn, oracle.linear(xf, packed, N, 3, bf))
+    return oracle.rel_l2(yn, oracle.linear(xf, packed, N, qt, bf))
 
 
 @pytest.mark.parametrize("dt", ["bf16", "f16"])
@@ -40,6 +40,14 @@ def _run(oracle, M, N, K, dt, bias=False, seed=0, rows=None):
                                    (300, 520, 1280), (512, 1024, 2048)])
 def test_shapes(oracle, dt, M, N, K):
     assert _run(oracle, M, N, K, dt, seed=M) <= TIGHT[dt]
+
+
+@pytest.mark.parametrize("qt", [0, 2, 16])
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+@pytest.mark.parametrize("M,N,K", [(16, 256, 64), (130, 300, 448), (300, 512, 1024)])
+def test_other_formats(oracle, qt, dt, M, N, K):
+    """Q4_0, Q8_0 and NF4 through the same tensor-core kernel (K a multiple of 64)."""
+    assert _run(oracle, M, N, K, dt, seed=M + qt, qt=qt) <= TIGHT[dt]
 
 
 def test_bias_and_ragged_edges(oracle):
