@@ -432,6 +432,88 @@ def run_prefill(args):
     print(json.dumps(line))
 
 
+FORMATS = {"q4_0": 0, "q8_0": 2, "q4_k": 3, "nf4": 16}
+
+
+def time_graph(step, K, W):
+    """Capture K calls of step(i) into one CUDA graph on a side stream and time one replay with
+    CUDA events (ms per step).  Removes the Python launch loop from small-kernel timings."""
+    import torch
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        for i in range(W):
+            step(i, side.cuda_stream)
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(K):
+                step(W + i, torch.cuda.current_stream().cuda_stream)
+        graph.replay()
+        side.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(side)
+        graph.replay()
+        e1.record(side)
+        side.synchronize()
+    return e0.elapsed_time(e1) / K, side
+
+
+def linear_case(fmt, M, N, K, steps, warmup, cache):
+    """One quantized linear Y[M,N] = X[M,K] W[N,K]^T: algorithmic GB/s and TFLOP/s."""
+    import torch
+    from mlxr_b200._capi import check, lib
+    from mlxr_b200.quantize import quantize
+    qt = FORMATS[fmt]
+    key = (fmt, N, K)
+    if key not in cache:
+        if ("w", N, K) not in cache:
+            cache[("w", N, K)] = (np.random.Generator(np.random.PCG64(SEED + 1)).standard_normal((N, K)) * 0.02).astype(np.float32)
+        packed = torch.from_numpy(quantize(cache[("w", N, K)], qt))
+        copies = max(2, int(np.ceil(400e6 / packed.numel()))) if M <= 64 else 1
+        cache[key] = [packed.cuda() for _ in range(min(copies, 16))]
+    ws = cache[key]
+    x = torch.from_numpy(np.random.Generator(np.random.PCG64(SEED + 4)).standard_normal((M, K)).astype(np.float32)).bfloat16().cuda()
+    y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    gs = lib.mlxr_default_group_size(qt)
+
+    def step(i, st):
+        check(lib.mlxr_q_gemm_dequant(x.data_ptr(), ws[i % len(ws)].data_ptr(), None, y.data_ptr(), M, N, K, qt, gs, 1, st))
+
+    ms, side = time_graph(step, steps, max(warmup, 3))
+    status = ctypes.c_int(0)
+    check(lib.mlxr_stream_status(side.cuda_stream, ctypes.byref(status)))
+    assert status.value == 0 and torch.isfinite(y.float()).all()
+    wbytes = ws[0].numel()
+    ab = wbytes + 2 * M * (K + N)
+    hbm, tf, which = measured_peaks()
+    gbs, tfl = ab / (ms * 1e-3) / 1e9, 2.0 * M * N * K / (ms * 1e-3) / 1e12
+    tensor_bound = 2.0 * M * N * K / (tf * 1e12) > ab / (hbm * 1e9)
+    return {"metric": "qlinear", "format": fmt, "M": M, "N": N, "K": K, "us": ms * 1e3, "GB/s": gbs, "TFLOP/s": tfl,
+            "bound": "tensor" if tensor_bound else "hbm", "frac": (tfl / tf) if tensor_bound else (gbs / hbm),
+            "peak_source": which, "weight_copies": len(ws)}
+
+
+def run_sweep(args):
+    """The format sweep and the decode / prefill linears of the Llama-3-8B shapes: one JSON line
+    per case (not the contract line; a measurement table for the design notes)."""
+    import torch
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    cache = {}
+    cases = []
+    for fmt in ("q8_0", "q4_0", "q4_k", "nf4"):
+        for M in (1, 16, 2048):
+            cases.append((fmt, M, 14336, 4096))
+    for M in (8, 32, 64, 512, 8192):
+        cases.append(("q4_k", M, 14336, 4096))
+    for M in (1, 8, 2048):
+        cases.append(("q4_k", M, 4096, 14336))
+    for fmt, M, N, K in cases:
+        steps = 200 if M <= 64 else 10
+        print(json.dumps(linear_case(fmt, M, N, K, steps, 5, cache)), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -443,7 +525,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--hidden", type=int, default=H)
     ap.add_argument("--inter", type=int, default=I)
-    ap.add_argument("--workload", default="mlp_decode", choices=["mlp_decode", "prefill"])
+    ap.add_argument("--workload", default="mlp_decode", choices=["mlp_decode", "prefill", "linear", "sweep"])
+    ap.add_argument("--format", default="q4_k", choices=["q4_0", "q8_0", "q4_k", "nf4"])
     ap.add_argument("--transpose", action="store_true", help="prefill: the down-projection shape (N = hidden, K = inter)")
     ap.add_argument("--exchange", default="auto", choices=["auto", "nccl_f32", "nccl_act", "peer"],
                     help="how the ranks' partial sums are added (N > 1)")
@@ -451,6 +534,13 @@ def main():
     SIZES["hidden"], SIZES["inter"] = args.hidden, args.inter
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "sweep":
+        run_sweep(args)
+    elif args.workload == "linear":
+        import torch
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        N, K = (SIZES["hidden"], SIZES["inter"]) if args.transpose else (SIZES["inter"], SIZES["hidden"])
+        print(json.dumps(linear_case(args.format, args.batch, N, K, min(args.steps, 500), args.warmup, {})))
     elif args.workload == "prefill":
         if args.batch == 1:
             args.batch = 2048

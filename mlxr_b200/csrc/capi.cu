@@ -137,6 +137,8 @@ static int run_linear(const void* x, const void* w, const void* bias, void* y, i
     L.w[0] = w; L.rows[0] = N; L.nmat = 1; L.K = K; L.x = x; L.y[0] = y; L.bias[0] = bias;
     return launch_decode(&L, 1, M, qt, dtype, ws->buf, kDecodeScratchBytes, ws->sync, &ws->bar_host, ws->status, st);
   }
+  if (M > 0 && N > 0 && gemv_rows_supported(qt, M, K, x, w) && !getenv("MLXR_NO_GEMV"))
+    return launch_gemv_rows(x, w, bias, y, M, N, K, qt, dtype, st);
   if (M > 0 && N > 0 && prefill_supported(qt, M, N, K, dtype, x, w, y) && !getenv("MLXR_NO_TC")) {
     Workspace* ws = nullptr;
     if (int r = get_workspace(st, 0, &ws)) return r;

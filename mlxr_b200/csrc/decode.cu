@@ -157,7 +157,7 @@ int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype
   // shared memory left for the x slice when the rings keep at least two stages per warp
   // two groups need room for 16 rings of at least two stages; otherwise run one group
   auto x_budget = [&](int ng) {
-    const int fixed = ng * kSlots * (kGroupWarps + 1) * kTileRows * MB * 4 + 1024 + 256;
+    const int fixed = ng * kSlots * (kGroupWarps + 1) * kTileRows * MB * 4 + 2048 + 256;
     return g_max_smem - 2 * ng * kGroupWarps * kStageBytes - fixed - M * 64 * (auxw + 1) * 4;
   };
   const int max_x = x_budget(NG);

@@ -121,18 +121,19 @@ __host__ __device__ inline SmemPlan make_plan(int ng, int stages, int max_slice_
   p.off_tile = p.off_slots + ng * kSlots * kGroupWarps * kTileRows * MB * 4;
   p.off_params = (p.off_tile + ng * kSlots * kTileRows * MB * 4 + 127) & ~127;
   p.off_misc = (p.off_params + (int)sizeof(Params) + 127) & ~127;
-  p.total = p.off_misc + 1024;
+  p.total = p.off_misc + 2048;
   return p;
 }
 
 struct Misc {
   unsigned long long full[2 * kGroupWarps][kMaxStages];   // one mbarrier per compute warp and stage
-  float redbuf[32];
+  float redbuf[2 * kGroupWarps * 8];   // per-warp, per-batch-row partial sums of squares
   int slot_free[2][kSlots];   // highest tile number that may write into the slot
   int slot_cnt[2][kSlots];    // warps that have delivered their partial sums for the slot's tile
+  float rinv[8];              // 1 / rms of each batch row (x prologue, batch > 2)
   int dead;
 };
-static_assert(sizeof(Misc) <= 1024, "Misc must fit its smem slot");
+static_assert(sizeof(Misc) <= 2048, "Misc must fit its smem slot");
 
 // ---- PTX wrappers ------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -262,6 +263,123 @@ __device__ __forceinline__ void x_prologue(const Phase& ph, const SmemPlan& plan
   uint32_t* aux = reinterpret_cast<uint32_t*>(smem + plan.off_aux);
   float* delta = reinterpret_cast<float*>(smem + plan.off_delta);
   const bool whole_row = (nseg * 256 == ph.K);
+  // Fixed-point conversion and stores of one (batch row, segment): v holds the segment's eight
+  // activations of this lane, already normalised and rounded to T.
+  auto emit = [&](int m, int sg, float (&v)[8]) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    // x ~ dl * xi with |xi| <= 32000; a non-finite block poisons its outputs with NaN
+    float dl = 1.0f, inv = 0.0f;
+    if (!(amax <= 3.0e38f)) { dl = __int_as_float(0x7fc00000); }
+    else if (amax > 0.0f) { dl = amax * (1.0f / 32000.0f); inv = 32000.0f / amax; }
+    int ssum = 0;
+    uint32_t hi_e = 0, hi_o = 0, lo_e = 0, lo_o = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      int q16 = __float2int_rn(v[i] * inv);
+      q16 = max(-32000, min(32000, q16));
+      ssum += q16;
+      const int h8 = (q16 + 128) >> 8, l8 = q16 - (h8 << 8);   // q16 = 256*h8 + l8, both in [-128,127]
+      const uint32_t hb = (uint32_t)(h8 & 0xFF), lb = (uint32_t)(l8 & 0xFF);
+      if (i & 1) { hi_o |= hb << (8 * (i >> 1)); lo_o |= lb << (8 * (i >> 1)); }
+      else       { hi_e |= hb << (8 * (i >> 1)); lo_e |= lb << (8 * (i >> 1)); }
+    }
+    // bytes of an 8-group are stored as (e0,e2,e4,e6 | e1,e3,e5,e7): the MMA k order
+    if constexpr (PAIRS) {
+      // sub-block lane/4 belongs to pair {0,1,0,0,2,3,2,2}[lane/4]; the other pairs' rows get zeros
+      const int myp = (0x22320010u >> (4 * (lane >> 2))) & 7;
+      uint8_t* xrow = smem + plan.off_x + (size_t)(8 * m) * plan.x_stride + sg * 256 + lane * 8;
+#pragma unroll
+      for (int p4 = 0; p4 < 4; p4++) {
+        const bool mine = p4 == myp;
+        *reinterpret_cast<uint2*>(xrow + (size_t)(2 * p4) * plan.x_stride) = mine ? make_uint2(hi_e, hi_o) : make_uint2(0u, 0u);
+        *reinterpret_cast<uint2*>(xrow + (size_t)(2 * p4 + 1) * plan.x_stride) = mine ? make_uint2(lo_e, lo_o) : make_uint2(0u, 0u);
+      }
+    } else {
+      uint8_t* xrow = smem + plan.off_x + (size_t)(2 * m) * plan.x_stride + sg * 256 + lane * 8;
+      *reinterpret_cast<uint2*>(xrow) = make_uint2(hi_e, hi_o);
+      *reinterpret_cast<uint2*>(xrow + plan.x_stride) = make_uint2(lo_e, lo_o);
+    }
+    // sums of xi per 32-element sub-block (4 lanes each)
+    ssum += __shfl_xor_sync(0xffffffffu, ssum, 1);
+    ssum += __shfl_xor_sync(0xffffffffu, ssum, 2);
+    int sb[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) sb[j] = __shfl_sync(0xffffffffu, ssum, 4 * j);
+    if (lane == 0) delta[m * plan.seg_stride + sg] = dl;
+    uint32_t* arow = aux + (size_t)m * plan.aux_stride + sg * AUXW;
+    if (lane < 4) {
+      if constexpr (PAIRS) {
+        // exact integer sums over the sub-blocks of each (scale, min) pair, as floats
+        const int ps = lane == 0 ? sb[0] + sb[2] + sb[3] : lane == 1 ? sb[1] : lane == 2 ? sb[4] + sb[6] + sb[7] : sb[5];
+        arow[lane] = __float_as_uint((float)ps);
+      } else if constexpr (QT == MLXR_Q4_K) {
+        // sums over the sub-blocks that share a (scale, min) pair, in units of 2^10
+        const int ps = lane == 0 ? sb[0] + sb[2] + sb[3] : lane == 1 ? sb[1] : lane == 2 ? sb[4] + sb[6] + sb[7] : sb[5];
+        const float f = (float)ps * (1.0f / 1024.0f);
+        const __half h = __float2half_rn(f);
+        arow[lane] = pack_half2(h, __float2half_rn(f - __half2float(h)));
+      } else {
+        // -8 * sum per sub-block in units of 2^10: word j = sub-blocks (2j, 2j+1); hi words, then lo words
+        const int a = lane == 0 ? sb[0] : lane == 1 ? sb[2] : lane == 2 ? sb[4] : sb[6];
+        const int b = lane == 0 ? sb[1] : lane == 1 ? sb[3] : lane == 2 ? sb[5] : sb[7];
+        const float fa = (float)a * (-8.0f / 1024.0f), fb = (float)b * (-8.0f / 1024.0f);
+        const __half ha = __float2half_rn(fa), hb2 = __float2half_rn(fb);
+        arow[lane] = pack_half2(ha, hb2);
+        arow[4 + lane] = pack_half2(__float2half_rn(fa - __half2float(ha)), __float2half_rn(fb - __half2float(hb2)));
+      }
+    }
+
+  };
+  if (M > 2) {
+    // ---- batch rows in parallel: (row, segment) items are dealt to the warps round-robin ----
+    if (gam) {
+      const int nrow = ph.K >> 8;
+      float part[8];
+#pragma unroll
+      for (int mm = 0; mm < 8; mm++) part[mm] = 0.0f;
+      for (int item = warp; item < M * nrow; item += nwarps) {
+        const int m = item / nrow, sgw = item - m * nrow;
+        float v[8];
+        load8(xg + (size_t)m * ph.K + sgw * 256 + lane * 8, v);
+        float q = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) q = fmaf(v[i], v[i], q);
+#pragma unroll
+        for (int mm = 0; mm < 8; mm++) part[mm] += (mm == m) ? q : 0.0f;
+      }
+#pragma unroll
+      for (int mm = 0; mm < 8; mm++) {
+        const float t = warp_sum(part[mm]);
+        if (lane == 0) misc->redbuf[warp * 8 + mm] = t;
+      }
+      __syncthreads();
+      if (tid < M) {
+        float tot = 0.0f;
+        for (int w = 0; w < nwarps; w++) tot += misc->redbuf[w * 8 + tid];
+        misc->rinv[tid] = 1.0f / sqrtf(tot / (float)ph.K + ph.eps);
+      }
+      __syncthreads();
+      tstamp(13);
+    }
+    for (int item = warp; item < M * nseg; item += nwarps) {
+      const int m = item / nseg, sg = item - m * nseg;
+      float v[8];
+      load8(xg + (size_t)m * ph.K + k0 + sg * 256 + lane * 8, v);
+      if (gam) {
+        float gv[8];
+        load8(gam + k0 + sg * 256 + lane * 8, gv);
+        const float rinv = misc->rinv[m];
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = Act<T>::to_f(Act<T>::from_f(__fmul_rn(__fmul_rn(v[i], rinv), gv[i])));
+      }
+      emit(m, sg, v);
+    }
+    return;
+  }
   for (int m = 0; m < M; m++) {
     const T* xrow_g = xg + (size_t)m * ph.K;
     float v0[8];            // first segment of this warp, kept across the reduction
@@ -328,72 +446,7 @@ __device__ __forceinline__ void x_prologue(const Phase& ph, const SmemPlan& plan
 #pragma unroll
         for (int i = 0; i < 8; i++) v[i] = Act<T>::to_f(Act<T>::from_f(__fmul_rn(__fmul_rn(v[i], rinv), gv[i])));
       }
-      float amax = 0.0f;
-#pragma unroll
-      for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-      // x ~ dl * xi with |xi| <= 32000; a non-finite block poisons its outputs with NaN
-      float dl = 1.0f, inv = 0.0f;
-      if (!(amax <= 3.0e38f)) { dl = __int_as_float(0x7fc00000); }
-      else if (amax > 0.0f) { dl = amax * (1.0f / 32000.0f); inv = 32000.0f / amax; }
-      int ssum = 0;
-      uint32_t hi_e = 0, hi_o = 0, lo_e = 0, lo_o = 0;
-#pragma unroll
-      for (int i = 0; i < 8; i++) {
-        int q16 = __float2int_rn(v[i] * inv);
-        q16 = max(-32000, min(32000, q16));
-        ssum += q16;
-        const int h8 = (q16 + 128) >> 8, l8 = q16 - (h8 << 8);   // q16 = 256*h8 + l8, both in [-128,127]
-        const uint32_t hb = (uint32_t)(h8 & 0xFF), lb = (uint32_t)(l8 & 0xFF);
-        if (i & 1) { hi_o |= hb << (8 * (i >> 1)); lo_o |= lb << (8 * (i >> 1)); }
-        else       { hi_e |= hb << (8 * (i >> 1)); lo_e |= lb << (8 * (i >> 1)); }
-      }
-      // bytes of an 8-group are stored as (e0,e2,e4,e6 | e1,e3,e5,e7): the MMA k order
-      if constexpr (PAIRS) {
-        // sub-block lane/4 belongs to pair {0,1,0,0,2,3,2,2}[lane/4]; the other pairs' rows get zeros
-        const int myp = (0x22320010u >> (4 * (lane >> 2))) & 7;
-        uint8_t* xrow = smem + plan.off_x + (size_t)(8 * m) * plan.x_stride + sg * 256 + lane * 8;
-#pragma unroll
-        for (int p4 = 0; p4 < 4; p4++) {
-          const bool mine = p4 == myp;
-          *reinterpret_cast<uint2*>(xrow + (size_t)(2 * p4) * plan.x_stride) = mine ? make_uint2(hi_e, hi_o) : make_uint2(0u, 0u);
-          *reinterpret_cast<uint2*>(xrow + (size_t)(2 * p4 + 1) * plan.x_stride) = mine ? make_uint2(lo_e, lo_o) : make_uint2(0u, 0u);
-        }
-      } else {
-        uint8_t* xrow = smem + plan.off_x + (size_t)(2 * m) * plan.x_stride + sg * 256 + lane * 8;
-        *reinterpret_cast<uint2*>(xrow) = make_uint2(hi_e, hi_o);
-        *reinterpret_cast<uint2*>(xrow + plan.x_stride) = make_uint2(lo_e, lo_o);
-      }
-      // sums of xi per 32-element sub-block (4 lanes each)
-      ssum += __shfl_xor_sync(0xffffffffu, ssum, 1);
-      ssum += __shfl_xor_sync(0xffffffffu, ssum, 2);
-      int sb[8];
-#pragma unroll
-      for (int j = 0; j < 8; j++) sb[j] = __shfl_sync(0xffffffffu, ssum, 4 * j);
-      if (lane == 0) delta[m * plan.seg_stride + sg] = dl;
-      uint32_t* arow = aux + (size_t)m * plan.aux_stride + sg * AUXW;
-      if (lane < 4) {
-        if constexpr (PAIRS) {
-          // exact integer sums over the sub-blocks of each (scale, min) pair, as floats
-          const int ps = lane == 0 ? sb[0] + sb[2] + sb[3] : lane == 1 ? sb[1] : lane == 2 ? sb[4] + sb[6] + sb[7] : sb[5];
-          arow[lane] = __float_as_uint((float)ps);
-        } else if constexpr (QT == MLXR_Q4_K) {
-          // sums over the sub-blocks that share a (scale, min) pair, in units of 2^10
-          const int ps = lane == 0 ? sb[0] + sb[2] + sb[3] : lane == 1 ? sb[1] : lane == 2 ? sb[4] + sb[6] + sb[7] : sb[5];
-          const float f = (float)ps * (1.0f / 1024.0f);
-          const __half h = __float2half_rn(f);
-          arow[lane] = pack_half2(h, __float2half_rn(f - __half2float(h)));
-        } else {
-          // -8 * sum per sub-block in units of 2^10: word j = sub-blocks (2j, 2j+1); hi words, then lo words
-          const int a = lane == 0 ? sb[0] : lane == 1 ? sb[2] : lane == 2 ? sb[4] : sb[6];
-          const int b = lane == 0 ? sb[1] : lane == 1 ? sb[3] : lane == 2 ? sb[5] : sb[7];
-          const float fa = (float)a * (-8.0f / 1024.0f), fb = (float)b * (-8.0f / 1024.0f);
-          const __half ha = __float2half_rn(fa), hb2 = __float2half_rn(fb);
-          arow[lane] = pack_half2(ha, hb2);
-          arow[4 + lane] = pack_half2(__float2half_rn(fa - __half2float(ha)), __float2half_rn(fb - __half2float(hb2)));
-        }
-      }
+      emit(m, sg, v);
     }
   }
 }

@@ -13,6 +13,9 @@ int launch_dequantize(const void* w, void* out, int N, int K, int qt, int out_dt
                       cudaStream_t st);
 int launch_qgemm_generic(const void* x, const void* w, const void* bias, void* y, int M, int N,
                          int K, int qt, int dtype, cudaStream_t st);
+bool gemv_rows_supported(int qt, int M, int K, const void* x, const void* w);
+int launch_gemv_rows(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int qt, int dtype,
+                     cudaStream_t st);
 int launch_linear_dense(const void* x, const void* w, const void* bias, void* y, int M, int N, int K,
                         int dtype, cudaStream_t st);
 int launch_rmsnorm(const void* x, const void* w, const void* res, void* y, int rows, int hidden,
