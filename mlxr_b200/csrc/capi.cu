@@ -42,6 +42,8 @@ struct Workspace {
   size_t bytes = 0;
   void* stage = nullptr;     // device staging of host-buffer calls
   size_t stage_bytes = 0;
+  void* part = nullptr;      // split-K partial sums of the tensor-core GEMM (never aliases buf)
+  size_t part_bytes = 0;
   uint32_t* sync = nullptr;  // kSyncWords zero-initialised words (counters, barriers)
   int* status = nullptr;     // device status word
   int* status_host = nullptr;  // pinned mirror
@@ -140,9 +142,14 @@ static int run_linear(const void* x, const void* w, const void* bias, void* y, i
   if (M > 0 && N > 0 && gemv_rows_supported(qt, M, K, x, w) && !getenv("MLXR_NO_GEMV"))
     return launch_gemv_rows(x, w, bias, y, M, N, K, qt, dtype, st);
   if (M > 0 && N > 0 && prefill_supported(qt, M, N, K, dtype, x, w, y) && !getenv("MLXR_NO_TC")) {
+    const int S = prefill_slices(M, N, K);
     Workspace* ws = nullptr;
     if (int r = get_workspace(st, 0, &ws)) return r;
-    return launch_prefill(x, w, bias, y, M, N, K, qt, dtype, ws->status, st);
+    if (S > 1) {
+      std::lock_guard<std::mutex> lk(g_ws_mu);
+      if (int r = grow(&ws->part, &ws->part_bytes, (size_t)S * M * N * sizeof(float), st)) return r;
+    }
+    return launch_prefill(x, w, bias, y, M, N, K, qt, dtype, ws->status, (float*)ws->part, ws->sync + 16, S, st);
   }
   return launch_qgemm_generic(x, w, bias, y, M, N, K, qt, dtype, st);
 }
@@ -529,6 +536,7 @@ int mlxr_release_workspaces(void) {
     cudaError_t e;
     if (ws.buf && (e = cudaFree(ws.buf)) != cudaSuccess && first == cudaSuccess) first = e;
     if (ws.stage && (e = cudaFree(ws.stage)) != cudaSuccess && first == cudaSuccess) first = e;
+    if (ws.part && (e = cudaFree(ws.part)) != cudaSuccess && first == cudaSuccess) first = e;
     if (ws.sync && (e = cudaFree(ws.sync)) != cudaSuccess && first == cudaSuccess) first = e;
     if (ws.status && (e = cudaFree(ws.status)) != cudaSuccess && first == cudaSuccess) first = e;
     if (ws.status_host) cudaFreeHost(ws.status_host);

@@ -58,7 +58,8 @@ int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype
 
 // ---- tensor-core GEMM for batch >= 9 on Q4_K with 16-bit activations (prefill.cu) -------------
 bool prefill_supported(int qt, int M, int N, int K, int dtype, const void* x, const void* w, const void* y);
+int prefill_slices(int M, int N, int K);     // K-slices (grid z); S > 1 needs S*M*N floats of scratch
 int launch_prefill(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int qt, int dtype,
-                   int* status, cudaStream_t st);
+                   int* status, float* partials, uint32_t* counters, int S, cudaStream_t st);
 
 }  // namespace mlxr

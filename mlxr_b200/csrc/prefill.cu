@@ -47,6 +47,9 @@ struct Params {
   int M, N, K;
   size_t row_bytes;
   int* status;
+  float* partials;    // split-K: [S][M][N] float partial sums (null when S == 1)
+  uint32_t* counters; // split-K: one arrival counter per output tile (self-clearing)
+  int S;              // K-slices = gridDim.z
   int debug;          // tuning probes: 1 skip the conversion math, 2 skip the weight loads
 };
 
@@ -248,8 +251,39 @@ struct Shared {
   uint64_t acc_full;
   uint32_t tmem_base;
   int dead;
+  int last;
   float nf4[16];
 };
+
+// 32 consecutive fp32 sums of output row m starting at column nc -> Y (+ bias), rounded to T
+template <typename T>
+__device__ __forceinline__ void store_row(const Params& P, int m, int nc, const uint32_t (&r)[32]) {
+  T* dst = reinterpret_cast<T*>(P.y) + (size_t)m * P.N + nc;
+  const T* bias = reinterpret_cast<const T*>(P.bias);
+  if (nc + 32 <= P.N && (P.N & 7) == 0) {
+#pragma unroll
+    for (int v4 = 0; v4 < 4; v4++) {
+      uint32_t pk[4];
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        float f0 = __uint_as_float(r[8 * v4 + 2 * e]), f1 = __uint_as_float(r[8 * v4 + 2 * e + 1]);
+        if (bias) { f0 += Act<T>::to_f(bias[nc + 8 * v4 + 2 * e]); f1 += Act<T>::to_f(bias[nc + 8 * v4 + 2 * e + 1]); }
+        const T t0 = Act<T>::from_f(f0), t1 = Act<T>::from_f(f1);
+        pk[e] = (uint32_t)(*reinterpret_cast<const unsigned short*>(&t0)) |
+                ((uint32_t)(*reinterpret_cast<const unsigned short*>(&t1)) << 16);
+      }
+      *reinterpret_cast<uint4*>(dst + 8 * v4) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    }
+  } else {
+    for (int e = 0; e < 32; e++) {
+      if (nc + e < P.N) {
+        float f = __uint_as_float(r[e]);
+        if (bias) f += Act<T>::to_f(bias[nc + e]);
+        dst[e] = Act<T>::from_f(f);
+      }
+    }
+  }
+}
 
 // MT accumulators (MT x 128 rows of X) per CTA, STAGES pipeline stages.
 // Warp 0: tensor-memory owner and MMA issuer (lane 0).  Warps 1..16: producers; thread pp of them
@@ -268,7 +302,10 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
   volatile int* dead = &sh->dead;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * (MT * kBM);
-  const int nkb = P.K / kBK;
+  // this CTA's K-slice: k-blocks [kb0, kb0 + nkb)
+  const int nkb_all = P.K / kBK;
+  const int kb0 = (int)(((long long)blockIdx.z * nkb_all) / P.S);
+  const int nkb = (int)(((long long)(blockIdx.z + 1) * nkb_all) / P.S) - kb0;
   constexpr uint32_t kCols = MT * kBN;        // TMEM columns (256 or 512: powers of two)
 
   if (tid >= 32 && tid < 48) sh->nf4[tid - 32] = kNF4[tid - 32];
@@ -326,20 +363,21 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     // k-block kb: super-block kb / 4, this thread's sub-block s = 2 * (kb % 4) + hb (16 bytes of nibbles)
     auto fetch = [&](int kb, uint4& q) {
       const uint8_t* blk = rowp + (size_t)(kb >> 2) * 144;
-      if ((kb & 3) == 0) hdr = __ldg(reinterpret_cast<const uint4*>(blk));
+      if ((kb & 3) == 0 || kb == kb0) hdr = __ldg(reinterpret_cast<const uint4*>(blk));
       q = __ldg(reinterpret_cast<const uint4*>(blk + 16 + 32 * (kb & 3) + 16 * hb));
     };
-    // nibbles are requested two k-blocks ahead (q0: even, q1: odd k-blocks); the header of a
+    // nibbles are requested two k-blocks ahead (q0: even, q1: odd steps); the header of a
     // super-block arrives with its first k-block and is copied out before the next one overwrites it
     const bool loads = live && !(P.debug & 2) && QT == MLXR_Q4_K;
     uint4 ch = make_uint4(0, 0, 0, 0);
-    if (loads) { fetch(0, q0); ch = hdr; if (nkb > 1) fetch(1, q1); }
+    if (loads) { fetch(kb0, q0); ch = hdr; if (nkb > 1) fetch(kb0 + 1, q1); }
     int issued = 0;
-    for (int kb = 0; kb < nkb; kb++) {
-      const int s = kb % STAGES, it = kb / STAGES;
-      const uint4 cq = (kb & 1) ? q1 : q0;
-      if ((kb & 3) == 0) ch = hdr;
-      if (loads && kb + 2 < nkb) { if (kb & 1) fetch(kb + 2, q1); else fetch(kb + 2, q0); }
+    for (int i = 0; i < nkb; i++) {
+      const int kb = kb0 + i;
+      const int s = i % STAGES, it = i / STAGES;
+      const uint4 cq = (i & 1) ? q1 : q0;
+      if ((kb & 3) == 0 || i == 0) ch = hdr;
+      if (loads && i + 2 < nkb) { if (i & 1) fetch(kb + 2, q1); else fetch(kb + 2, q0); }
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->empty[s]), (it & 1) ^ 1, dead))) break;   // warp-uniform
       if (tma_thread) {
         const uint32_t bar = smem_u32(&sh->full_a[s]);
@@ -347,7 +385,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
 #pragma unroll
         for (int a = 0; a < MT; a++)
           tma_load_2d(smem_u32(smem + (size_t)s * kStageBytes + a * kATile), &xmap, kb * kBK, m0 + a * kBM, bar);
-        issued = kb + 1;
+        issued = i + 1;
       }
       uint8_t* brow = smem + (size_t)s * kStageBytes + MT * kATile + (size_t)p * 128;
       uint4 o[4];
@@ -396,9 +434,9 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     }
     if (tma_thread && *dead) {
       // copies in flight must land before the CTA may exit (bounded)
-      for (int kb = max(0, issued - STAGES); kb < issued; kb++) {
-        const uint32_t bar = smem_u32(&sh->full_a[kb % STAGES]);
-        for (uint32_t i = 0; i < kSpin; i++) if (mbar_try(bar, (kb / STAGES) & 1)) break;
+      for (int j = max(0, issued - STAGES); j < issued; j++) {
+        const uint32_t bar = smem_u32(&sh->full_a[j % STAGES]);
+        for (uint32_t sp = 0; sp < kSpin; sp++) if (mbar_try(bar, (j / STAGES) & 1)) break;
       }
     }
     __syncwarp();
@@ -407,8 +445,6 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     if (__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->acc_full), 0, dead))) {   // warp-uniform: tcgen05.ld is .aligned
       tc_fence_after();
       const int quarter = warp & 3, gi = (warp - 1) >> 2;
-      T* yb = reinterpret_cast<T*>(P.y);
-      const T* bias = reinterpret_cast<const T*>(P.bias);
 #pragma unroll 1
       for (int u = gi; u < MT * (kBN / 32); u += 4) {
         const int a = u / (kBN / 32), chn = u % (kBN / 32);
@@ -417,32 +453,23 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * kBN + chn * 32), r);
         const int nc = n0 + chn * 32;
         if (m < P.M) {
-          T* dst = yb + (size_t)m * P.N + nc;
-          if (nc + 32 <= P.N && (P.N & 7) == 0) {
-#pragma unroll
-            for (int v4 = 0; v4 < 4; v4++) {
-              uint32_t pk[4];
-#pragma unroll
-              for (int e = 0; e < 4; e++) {
-                float f0 = __uint_as_float(r[8 * v4 + 2 * e]), f1 = __uint_as_float(r[8 * v4 + 2 * e + 1]);
-                if (bias) { f0 += Act<T>::to_f(bias[nc + 8 * v4 + 2 * e]); f1 += Act<T>::to_f(bias[nc + 8 * v4 + 2 * e + 1]); }
-                const T t0 = Act<T>::from_f(f0), t1 = Act<T>::from_f(f1);
-                pk[e] = (uint32_t)(*reinterpret_cast<const unsigned short*>(&t0)) |
-                        ((uint32_t)(*reinterpret_cast<const unsigned short*>(&t1)) << 16);
-              }
-              *reinterpret_cast<uint4*>(dst + 8 * v4) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            }
+          if (P.S == 1) {
+            store_row<T>(P, m, nc, r);
           } else {
-            for (int e = 0; e < 32; e++) {
-              if (nc + e < P.N) {
-                float f = __uint_as_float(r[e]);
-                if (bias) f += Act<T>::to_f(bias[nc + e]);
-                dst[e] = Act<T>::from_f(f);
-              }
+            // split-K: park this slice's sums; the last slice to arrive adds them up below
+            float* dst = P.partials + ((size_t)blockIdx.z * P.M + m) * P.N + nc;
+            if (nc + 32 <= P.N && (P.N & 3) == 0) {
+#pragma unroll
+              for (int v4 = 0; v4 < 8; v4++)
+                __stcg(reinterpret_cast<float4*>(dst) + v4, make_float4(__uint_as_float(r[4 * v4]), __uint_as_float(r[4 * v4 + 1]),
+                                                                       __uint_as_float(r[4 * v4 + 2]), __uint_as_float(r[4 * v4 + 3])));
+            } else {
+              for (int e = 0; e < 32; e++) if (nc + e < P.N) __stcg(dst + e, __uint_as_float(r[e]));
             }
           }
         }
       }
+      if (P.S > 1) __threadfence();
     }
   }
   tc_fence_before();
@@ -452,6 +479,48 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     tmem_dealloc(tmem, kCols);
   }
   if (tid == 0 && sh->dead) atomicExch(P.status, MLXR_ERR_TIMEOUT);
+  if (P.S > 1) {
+    // every warp's partial stores were fenced before the barrier above; the last slice of this
+    // output tile adds the S slices in slice order (deterministic) and stores Y
+    if (tid == 0) {
+      const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+      const uint32_t prev = atomicAdd(P.counters + tile, 1u);
+      const int last = (prev == (uint32_t)P.S - 1u) && !sh->dead;
+      if (prev == (uint32_t)P.S - 1u) P.counters[tile] = 0u;     // self-clearing for the next launch
+      __threadfence();
+      sh->last = last;
+    }
+    __syncthreads();
+    if (sh->last && warp >= 1) {
+      const int quarter = warp & 3, gi = (warp - 1) >> 2;
+#pragma unroll 1
+      for (int u = gi; u < MT * (kBN / 32); u += 4) {
+        const int a = u / (kBN / 32), chn = u % (kBN / 32);
+        const int m = m0 + a * kBM + quarter * 32 + lane;
+        const int nc = n0 + chn * 32;
+        if (m >= P.M) continue;
+        uint32_t r[32];
+#pragma unroll
+        for (int e = 0; e < 32; e++) r[e] = 0u;
+        for (int z = 0; z < P.S; z++) {
+          const float* src = P.partials + ((size_t)z * P.M + m) * P.N + nc;
+          if (nc + 32 <= P.N && (P.N & 3) == 0) {
+#pragma unroll
+            for (int v4 = 0; v4 < 8; v4++) {
+              const float4 f = __ldcg(reinterpret_cast<const float4*>(src) + v4);
+              r[4 * v4] = __float_as_uint(__uint_as_float(r[4 * v4]) + f.x);
+              r[4 * v4 + 1] = __float_as_uint(__uint_as_float(r[4 * v4 + 1]) + f.y);
+              r[4 * v4 + 2] = __float_as_uint(__uint_as_float(r[4 * v4 + 2]) + f.z);
+              r[4 * v4 + 3] = __float_as_uint(__uint_as_float(r[4 * v4 + 3]) + f.w);
+            }
+          } else {
+            for (int e = 0; e < 32; e++) if (nc + e < P.N) r[e] = __float_as_uint(__uint_as_float(r[e]) + __ldcg(src + e));
+          }
+        }
+        store_row<T>(P, m, nc, r);
+      }
+    }
+  }
 }
 
 }  // namespace prefill
@@ -509,14 +578,26 @@ static int launch_tc(const CUtensorMap& xmap, const prefill::Params& P, cudaStre
     MLXR_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_done[dev & 63] = true;
   }
-  dim3 grid((P.N + kBN - 1) / kBN, (P.M + MT * kBM - 1) / (MT * kBM));
+  dim3 grid((P.N + kBN - 1) / kBN, (P.M + MT * kBM - 1) / (MT * kBM), P.S);
   kern<<<grid, kThreads, smem, st>>>(xmap, P);
   MLXR_LAUNCH_CHECK("qgemm_tc_kernel");
   return MLXR_OK;
 }
 
+// K-slices for a launch: only when one row of tiles (M <= 128) leaves most SMs idle.
+int prefill_slices(int M, int N, int K) {
+  if (M > prefill::kBM) return 1;
+  int sms = 148;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int ntiles = (N + prefill::kBN - 1) / prefill::kBN, nkb = K / prefill::kBK;
+  int S = 1;
+  while (S < 8 && ntiles * (S * 2) <= sms && nkb / (S * 2) >= 4) S *= 2;
+  return S;
+}
+
 int launch_prefill(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int qt, int dtype,
-                   int* status, cudaStream_t st) {
+                   int* status, float* partials, uint32_t* counters, int S, cudaStream_t st) {
   CUtensorMap xmap;
   if (int r = x_tensor_map(x, M, K, dtype, &xmap)) return r;
   prefill::Params P;
@@ -526,6 +607,9 @@ int launch_prefill(const void* x, const void* w, const void* bias, void* y, int 
   P.M = M; P.N = N; P.K = K;
   P.row_bytes = (size_t)(K / block_elems(qt)) * block_bytes(qt);
   P.status = status;
+  P.partials = S > 1 ? partials : nullptr;
+  P.counters = counters;
+  P.S = S;
   P.debug = 0;
   if (const char* e = getenv("MLXR_TC_DEBUG")) P.debug = atoi(e);   // tuning probe
   const bool two = M > prefill::kBM;      // a second accumulator only pays when there are rows for it

@@ -50,6 +50,17 @@ def test_other_formats(oracle, qt, dt, M, N, K):
     assert _run(oracle, M, N, K, dt, seed=M + qt, qt=qt) <= TIGHT[dt]
 
 
+@pytest.mark.parametrize("M,N,K", [(16, 256, 2048), (33, 1024, 4096), (128, 300, 1536), (64, 4096, 14336)])
+def test_split_k_small_batches(oracle, M, N, K):
+    """One row of output tiles: the K range is split over CTAs and the last slice reduces."""
+    import mlxr_b200 as mx
+    assert mx._capi.lib.mlxr_version()  # library loaded
+    rows = np.arange(M) if M * N * K < 3e8 else np.array([0, 1, M // 2, M - 1])
+    assert _run(oracle, M, N, K, "bf16", seed=3, rows=rows, bias=(N == 300)) <= TIGHT["bf16"]
+    # twice in a row: the tile counters must have cleared themselves
+    assert _run(oracle, M, N, K, "bf16", seed=3, rows=rows) <= TIGHT["bf16"]
+
+
 def test_bias_and_ragged_edges(oracle):
     assert _run(oracle, 70, 264, 512, "f16", bias=True) <= TIGHT["f16"]
     assert _run(oracle, 257, 8, 256, "bf16", bias=True) <= TIGHT["bf16"]
