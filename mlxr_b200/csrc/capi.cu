@@ -154,6 +154,24 @@ static int run_linear(const void* x, const void* w, const void* bias, void* y, i
   return launch_qgemm_generic(x, w, bias, y, M, N, K, qt, dtype, st);
 }
 
+int mlp_block_tp_fused(const void* x, const void* norm_weight, const void* w_gate, const void* w_up, const void* w_down,
+                       int M, int hidden, int inter, int qt, float eps, int dtype, const DecodeTp* tp, cudaStream_t st) {
+  const void* wgu[2] = {w_gate, w_up};
+  if (M < 1 || !decode_supported(qt, M, hidden, wgu, 2) || !decode_supported(qt, M, inter, &w_down, 1)) return MLXR_ERR_UNSUPPORTED;
+  Workspace* ws = nullptr;
+  const size_t i_bytes = align_up((size_t)M * inter * dtype_size(dtype), 256);
+  if (int r = get_workspace(st, kDecodeScratchBytes + i_bytes, &ws)) return r;
+  char* base = (char*)ws->buf + kDecodeScratchBytes;
+  DecodeLinear L[2];
+  memset(L, 0, sizeof(L));
+  L[0].w[0] = w_gate; L[0].w[1] = w_up; L[0].rows[0] = L[0].rows[1] = inter; L[0].nmat = 2;
+  L[0].interleave = 1; L[0].K = hidden; L[0].x = x; L[0].gamma = norm_weight; L[0].eps = eps;
+  L[0].y[0] = base;
+  L[1].w[0] = w_down; L[1].rows[0] = hidden; L[1].nmat = 1; L[1].K = inter; L[1].x = base; L[1].y[0] = tp->y;
+  L[1].epi[0] = 3;
+  return launch_decode(L, 2, M, qt, dtype, ws->buf, kDecodeScratchBytes, ws->sync, &ws->bar_host, ws->status, st, tp);
+}
+
 }  // namespace mlxr
 
 using namespace mlxr;

@@ -133,7 +133,8 @@ static int launch_inst(const Params& P, const SmemPlan& plan, int G, bool cooper
 // Launch one or two chained phases.  sync: workspace sync words (zero-initialised once);
 // word 0 is the grid-barrier counter whose host mirror is *bar_host.
 int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype, void* scratch,
-                  size_t scratch_bytes, uint32_t* sync, uint32_t* bar_host, int* status, cudaStream_t st) {
+                  size_t scratch_bytes, uint32_t* sync, uint32_t* bar_host, int* status, cudaStream_t st,
+                  const DecodeTp* tp) {
   if (int r = device_props()) return r;
   Params P;
   memset(&P, 0, sizeof(P));
@@ -144,6 +145,20 @@ int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype
   if (const char* e = getenv("MLXR_DEC_FLAGS")) P.flags = (uint32_t)atoi(e);   // tuning override
   P.status = status;
   P.trace = g_trace;
+  P.tp_world = 0;
+  if (tp && tp->world > 1) {
+    const DecodeLinear& last = lin[nphases - 1];
+    if (last.nmat != 1 || last.interleave || last.epi[0] != 3 || (size_t)M * last.rows[0] > kTpSlotElems ||
+        (last.rows[0] + kTileRows - 1) / kTileRows > kTpFlagsPerRank) {
+      set_error("decode kernel: this shape cannot take the fused exchange");
+      return MLXR_ERR_UNSUPPORTED;
+    }
+    for (int i = 0; i < kTpMaxWorld; i++) P.tp_peer[i] = tp->peer[i];
+    P.tp_rank = tp->rank;
+    P.tp_world = tp->world;
+    P.tp_ctl = tp->ctl;
+    P.tp_y = tp->y;
+  }
   // batch <= 2 with Q4_K: pairs in the MMA columns, one n-tile per batch row
   bool pairs = (qt == MLXR_Q4_K && M <= 2);
   if (const char* e = getenv("MLXR_DEC_PAIRS")) pairs = pairs && atoi(e) != 0;  // tuning override
@@ -192,7 +207,7 @@ int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype
     if (S <= 0) {
       if (NG == 2 && !getenv("MLXR_DEC_GROUPS")) {   // not enough shared memory beside 16 rings: one group
         setenv("MLXR_DEC_GROUPS", "1", 1);
-        const int rc1 = launch_decode(lin, nphases, M, qt, dtype, scratch, scratch_bytes, sync, bar_host, status, st);
+        const int rc1 = launch_decode(lin, nphases, M, qt, dtype, scratch, scratch_bytes, sync, bar_host, status, st, tp);
         unsetenv("MLXR_DEC_GROUPS");
         return rc1;
       }

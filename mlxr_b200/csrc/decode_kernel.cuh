@@ -35,6 +35,7 @@
 #include <cuda.h>   // CUtensorMap (type only; the encoder is fetched at run time)
 
 #include "common.cuh"
+#include "kernels.h"
 
 namespace mlxr {
 namespace decode {
@@ -95,7 +96,19 @@ struct Params {
   uint32_t flags;        // bit 0: request x before the weight stream (no overlap with the previous kernel's tail)
   int* status;
   unsigned long long* trace;  // optional: 16 globaltimer stamps per CTA (null = off)
+  // tensor-parallel exchange fused into the last phase (world <= 1: off)
+  char* tp_peer[kTpMaxWorld];
+  int tp_rank, tp_world;
+  uint32_t* tp_ctl;
+  void* tp_y;
 };
+
+__device__ __forceinline__ float* tp_slot(char* base, int parity, int src) {
+  return reinterpret_cast<float*>(base + kTpFlagBytes) + ((size_t)parity * kTpMaxWorld + src) * kTpSlotElems;
+}
+__device__ __forceinline__ uint32_t* tp_flag(char* base, int src, int idx) {
+  return reinterpret_cast<uint32_t*>(base) + src * kTpFlagsPerRank + idx;
+}
 
 // Shared-memory plan (bytes), identical on host and device.
 struct SmemPlan {
@@ -651,7 +664,8 @@ __device__ __forceinline__ void segment_mma_pairs(const uint8_t* rl, const uint8
 // ---- tile epilogue (one warp) --------------------------------------------------------------
 // tile[row][col] holds the complete sums of this CTA's K-slice for 16 rows x MB batch columns.
 template <typename T, int MB>
-__device__ __forceinline__ void tile_epilogue(const Params& P, const Phase& ph, float* tile, int t, int ks, int lane) {
+__device__ __forceinline__ void tile_epilogue(const Params& P, const Phase& ph, float* tile, int t, int ks, int lane,
+                                              uint32_t tp_seq) {
   const int M = P.M;
   bool do_epilogue = true;
   if (ph.S > 1) {
@@ -704,9 +718,19 @@ __device__ __forceinline__ void tile_epilogue(const Params& P, const Phase& ph, 
       const T* bias = reinterpret_cast<const T*>(ph.bias[mat]);
       if (bias) { ve += Act<T>::to_f(bias[R]); if (has_odd) vo += Act<T>::to_f(bias[R + 1]); }
       if (ph.epi[mat] == kEpiF32) {
-        float* of = reinterpret_cast<float*>(ph.y[mat]) + (size_t)m * ph.rows[mat] + R;
-        of[0] = ve;
-        if (has_odd) of[1] = vo;
+        const size_t off = (size_t)m * ph.rows[mat] + R;
+        if (P.tp_world > 1) {
+          // straight into slot `rank` of every rank's exchange buffer (plain peer stores)
+          for (int pr = 0; pr < P.tp_world; pr++) {
+            float* of = tp_slot(P.tp_peer[(P.tp_rank + 1 + pr) % P.tp_world], (int)(tp_seq & 1u), P.tp_rank) + off;
+            of[0] = ve;
+            if (has_odd) of[1] = vo;
+          }
+        } else {
+          float* of = reinterpret_cast<float*>(ph.y[mat]) + off;
+          of[0] = ve;
+          if (has_odd) of[1] = vo;
+        }
         continue;
       }
       T* out = reinterpret_cast<T*>(ph.y[mat]) + (size_t)m * ph.rows[mat] + R;
@@ -722,6 +746,15 @@ __device__ __forceinline__ void tile_epilogue(const Params& P, const Phase& ph, 
       } else {
         out[0] = Act<T>::from_f(ve);
         if (has_odd) out[1] = Act<T>::from_f(vo);
+      }
+    }
+    if (P.tp_world > 1 && ph.epi[0] == kEpiF32 && ph.S > 1) {
+      // K split over CTAs: which CTA finishes a tile differs from rank to rank, so the flag is
+      // per tile: the warp's stores to the peers, then this tile's flag there (release at system scope)
+      __syncwarp();
+      if (lane < P.tp_world) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(tp_flag(P.tp_peer[lane], P.tp_rank, t)), "r"(tp_seq) : "memory");
       }
     }
   }
@@ -871,6 +904,9 @@ decode_kernel(const __grid_constant__ Params Pg, const __grid_constant__ SmemPla
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   asm volatile("griddepcontrol.wait;" ::: "memory");
   stamp(12);
+  // tensor-parallel exchange: this launch's sequence number (stable: the previous launch is complete)
+  uint32_t tp_seq = 0;
+  if (P.tp_world > 1) tp_seq = *reinterpret_cast<volatile uint32_t*>(P.tp_ctl) + 1u;
   // x (and gamma) of batch 0 for this warp's first segment are requested up front so that
   // their latency overlaps the set-up below
   float pre[8] = {0, 0, 0, 0, 0, 0, 0, 0}, gpre[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -1037,15 +1073,79 @@ decode_kernel(const __grid_constant__ Params Pg, const __grid_constant__ SmemPla
             __threadfence_block();
             *reinterpret_cast<volatile int*>(&misc->slot_free[group][slot]) = qg + kSlots;
           }
-          tile_epilogue<T, MB>(P, ph, tile, t, ks, lane);
+          tile_epilogue<T, MB>(P, ph, tile, t, ks, lane, tp_seq);
           __syncwarp();
         }
       }
     }
   }
   stamp(15);
+  if (P.tp_world > 1) {
+    // ---- reduction of the tensor-parallel block: output tile t is summed by CTA t mod G, one warp
+    // per tile, once every rank's flag for the tile has arrived (bounded wait); ranks are added
+    // in rank order, so all ranks store bit-identical results ----
+    const Phase& ph = P.ph[P.nphases - 1];
+    char* mine = P.tp_peer[P.tp_rank];
+    const int parity = (int)(tp_seq & 1u);
+    // Without a K split the tile -> CTA map is the same on every rank: one flag per CTA, raised
+    // once after all of its tiles (a single system-scope fence, after the rings have drained),
+    // and a CTA reduces exactly the tiles it produced.  Flag indices: CTA c, or tile t when split.
+    const bool per_cta = ph.S == 1;
+    if (per_cta) {
+      __syncthreads();
+      if (tid < P.tp_world) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(tp_flag(P.tp_peer[tid], P.tp_rank, cta)), "r"(tp_seq) : "memory");
+      }
+    }
+    // tiles this CTA reduces: its own (both groups' lanes) without a K split, else t = cta, cta + G, ..
+    const int n_mine = per_cta ? tile_lane(ph, cta, G, 0, NG).count + (NG > 1 ? tile_lane(ph, cta, G, NG - 1, NG).count : 0)
+                               : (ph.ntiles > cta ? (ph.ntiles - cta + G - 1) / G : 0);
+    for (int k = 0; k < n_mine; k++) {
+      int t;
+      if (per_cta) {
+        const int c0 = tile_lane(ph, cta, G, 0, NG).count;
+        const TileLane tl = tile_lane(ph, cta, G, k < c0 ? 0 : NG - 1, NG);
+        t = tl.first + (k < c0 ? k : k - c0) * tl.step;
+      } else {
+        t = cta + k * G;
+      }
+      if (k % kAllWarps != warp) continue;
+      bool ok = true;
+      if (lane < P.tp_world) {
+        const uint32_t* f = tp_flag(mine, lane, per_cta ? cta : t);
+        ok = false;
+        for (uint32_t i = 0; i < kSpinLimit; i++) {
+          uint32_t v;
+          asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+          if ((int32_t)(v - tp_seq) >= 0) { ok = true; break; }
+        }
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { misc->dead = 1; continue; }
+      T* yf = reinterpret_cast<T*>(P.tp_y);
+      for (int e = lane; e < kTileRows * M; e += 32) {
+        const int r = e % kTileRows, m = e / kTileRows;
+        const int R = kTileRows * t + r;
+        if (R >= ph.n_total) continue;
+        const size_t off = (size_t)m * ph.n_total + R;
+        float acc = 0.0f;
+        for (int src = 0; src < P.tp_world; src++) acc += __ldcg(tp_slot(mine, parity, src) + off);
+        yf[off] = Act<T>::from_f(acc);
+      }
+    }
+  }
   __syncthreads();
   if (tid == 0 && misc->dead) atomicExch(P.status, MLXR_ERR_TIMEOUT);
+  if (P.tp_world > 1 && tid == 0) {
+    // the last CTA to finish advances the sequence number for the next launch
+    __threadfence();
+    if (atomicAdd(P.tp_ctl + 1, 1u) == (uint32_t)G - 1u) {
+      P.tp_ctl[1] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(P.tp_ctl) = tp_seq;
+    }
+  }
 }
 
 }  // namespace decode

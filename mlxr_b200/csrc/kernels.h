@@ -30,6 +30,24 @@ int launch_rope(const void* x, const uint16_t* cos_t, const uint16_t* sin_t,
                 int max_seq, int mode, float scale, int offset, int dtype, int* status,
                 cudaStream_t st);
 
+// ---- exchange buffer of the tensor-parallel block (tp.cu, decode_kernel.cuh) -------------------
+// One per rank, mapped by every peer:
+// [flags: kTpMaxWorld x kTpFlagsPerRank uint32][pad to kTpFlagBytes][slots: 2 parities x kTpMaxWorld x kTpSlotElems float]
+constexpr int kTpMaxWorld = 8;
+constexpr int kTpFlagsPerRank = 1024;              // indexed by CTA (exchange kernel) or by output tile (fused decode)
+constexpr size_t kTpSlotElems = 256 * 1024;        // = MLXR_TP_PEER_MAX_ELEMS
+constexpr size_t kTpFlagBytes = 64 * 1024;
+constexpr size_t kTpXchgBytes = kTpFlagBytes + 2 * kTpMaxWorld * kTpSlotElems * sizeof(float);
+// What the decode kernel needs to push its partial sums to the peers and reduce: every rank's
+// exchange buffer as mapped in this process, this rank, the world size, the sequence words
+// ([0] sequence number, [1] CTAs finished) and the final output [M, hidden] of the activation dtype.
+struct DecodeTp {
+  char* peer[kTpMaxWorld];
+  int rank, world;
+  uint32_t* ctl;
+  void* y;
+};
+
 // ---- persistent decode kernel (decode.cu) ---------------------------------------------------
 // One linear (or up to three stacked along N, or gate/up interleaved) of a decode phase.
 struct DecodeLinear {
@@ -53,8 +71,16 @@ constexpr size_t kDecodeScratchBytes = (size_t)8 << 20;  // split-K partial sums
 void set_decode_trace(void* dev_ptr);
 void set_decode_launch_mode(int mode);
 bool decode_supported(int qt, int M, int K, const void* const* w, int nmat);
+// tp (optional): the last phase must be a single plain linear with epi 3 (float partial sums); its
+// sums then go straight into the peers' exchange buffers and the kernel ends with the reduction.
 int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype, void* scratch,
-                  size_t scratch_bytes, uint32_t* sync, uint32_t* bar_host, int* status, cudaStream_t st);
+                  size_t scratch_bytes, uint32_t* sync, uint32_t* bar_host, int* status, cudaStream_t st,
+                  const DecodeTp* tp = nullptr);
+// The tensor-parallel block in one launch when the decode kernel takes the shapes (else MLXR_ERR_UNSUPPORTED
+// and nothing is launched): inter_local is this rank's share of the intermediate size.
+int mlp_block_tp_fused(const void* x, const void* norm_weight, const void* w_gate, const void* w_up, const void* w_down,
+                       int M, int hidden, int inter_local, int qt, float eps, int dtype, const DecodeTp* tp,
+                       cudaStream_t st);
 
 // ---- tensor-core GEMM for batch >= 9 on Q4_K with 16-bit activations (prefill.cu) -------------
 bool prefill_supported(int qt, int M, int N, int K, int dtype, const void* x, const void* w, const void* y);

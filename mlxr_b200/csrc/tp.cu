@@ -66,12 +66,14 @@ ncclDataType_t nccl_dtype(int dtype) {
 }
 
 // ---- exchange buffer layout (one per rank, mapped by every peer) --------------------------------
-// [flags: kMaxWorld x kMaxCtas uint32][pad to 64 KB][slots: 2 parities x kMaxWorld x kSlotElems float]
-constexpr int kMaxWorld = 8;
-constexpr int kMaxCtas = 256;
-constexpr size_t kSlotElems = MLXR_TP_PEER_MAX_ELEMS;
-constexpr size_t kFlagBytes = 64 * 1024;
-constexpr size_t kXchgBytes = kFlagBytes + 2 * kMaxWorld * kSlotElems * sizeof(float);
+// layout constants shared with the decode kernel's fused exchange (kernels.h)
+constexpr int kMaxWorld = kTpMaxWorld;
+constexpr int kMaxCtas = 256;                      // CTAs of the exchange kernel (flag index < kTpFlagsPerRank)
+constexpr size_t kSlotElems = kTpSlotElems;
+constexpr size_t kFlagBytes = kTpFlagBytes;
+constexpr size_t kXchgBytes = kTpXchgBytes;
+static_assert(kTpSlotElems == MLXR_TP_PEER_MAX_ELEMS, "header and kernel disagree on the slot size");
+static_assert(kMaxCtas <= kTpFlagsPerRank, "flag index range");
 constexpr uint32_t kPeerSpinLimit = 1u << 24;   // bounded wait on a peer's flag
 
 struct PeerTable {
@@ -82,7 +84,7 @@ __device__ __forceinline__ float* slot_ptr(char* base, int parity, int src) {
   return reinterpret_cast<float*>(base + kFlagBytes) + ((size_t)parity * kMaxWorld + src) * kSlotElems;
 }
 __device__ __forceinline__ uint32_t* flag_ptr(char* base, int src, int cta) {
-  return reinterpret_cast<uint32_t*>(base) + src * kMaxCtas + cta;
+  return reinterpret_cast<uint32_t*>(base) + src * kTpFlagsPerRank + cta;
 }
 
 // One-shot all-reduce.  CTA b owns elements [b*chunk, (b+1)*chunk): it stores its rank's values
@@ -377,6 +379,20 @@ int mlxr_tp_mlp_block(mlxr_tp_ctx* c, const void* x, const void* norm_weight, co
   }
   if (M == 0) return MLXR_OK;
   const size_t n = (size_t)M * hidden;
+  if (c->world > 1 && c->xchg && (exchange == MLXR_TP_EXCHANGE_AUTO || exchange == MLXR_TP_EXCHANGE_PEER) &&
+      n <= kSlotElems && !getenv("MLXR_TP_NO_FUSE")) {
+    // decode shapes: one launch computes the rank's share, stores its sums into every rank's
+    // exchange buffer from the epilogue and ends with the reduction
+    DecodeTp tp;
+    for (int i = 0; i < kMaxWorld; i++) tp.peer[i] = c->peers.base[i];
+    tp.rank = c->rank;
+    tp.world = c->world;
+    tp.ctl = c->ctl;
+    tp.y = y;
+    const int rc = mlp_block_tp_fused(x, norm_weight, wg, wu, wd, M, hidden, inter / c->world, qt, eps, dtype, &tp,
+                                      (cudaStream_t)stream);
+    if (rc != MLXR_ERR_UNSUPPORTED) return rc;
+  }
   // the NCCL float path reduces out of place into a second region of the partial buffer
   if (int r = ensure_partial(c, 2 * n > kSlotElems ? 2 * n : kSlotElems)) return r;
   if (int r = mlxr_mlp_block_partial_f32(x, norm_weight, wg, wu, wd, c->partial, M, hidden, inter / c->world, qt,
