@@ -132,9 +132,20 @@ static int launch_inst(const Params& P, const SmemPlan& plan, int G, bool cooper
 
 // Launch one or two chained phases.  sync: workspace sync words (zero-initialised once);
 // word 0 is the grid-barrier counter whose host mirror is *bar_host.
+static int launch_decode_impl(const DecodeLinear* lin, int nphases, int M, int qt, int dtype, void* scratch,
+                              size_t scratch_bytes, uint32_t* sync, uint32_t* bar_host, int* status, cudaStream_t st,
+                              const DecodeTp* tp, int force_groups);
+
 int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype, void* scratch,
                   size_t scratch_bytes, uint32_t* sync, uint32_t* bar_host, int* status, cudaStream_t st,
                   const DecodeTp* tp) {
+  return launch_decode_impl(lin, nphases, M, qt, dtype, scratch, scratch_bytes, sync, bar_host, status, st, tp, 0);
+}
+
+// force_groups: 0 = choose, 1 or 2 = that many warp groups per CTA
+static int launch_decode_impl(const DecodeLinear* lin, int nphases, int M, int qt, int dtype, void* scratch,
+                              size_t scratch_bytes, uint32_t* sync, uint32_t* bar_host, int* status, cudaStream_t st,
+                              const DecodeTp* tp, int force_groups) {
   if (int r = device_props()) return r;
   Params P;
   memset(&P, 0, sizeof(P));
@@ -164,17 +175,33 @@ int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype
   if (const char* e = getenv("MLXR_DEC_PAIRS")) pairs = pairs && atoi(e) != 0;  // tuning override
   const int NT = pairs ? M : (M <= 4 ? 1 : 2);
   const int xrows = pairs ? 8 : 2;
-  int NG = 2;
-  if (const char* e = getenv("MLXR_DEC_GROUPS")) { const int v = atoi(e); if (v == 1 || v == 2) NG = v; }  // tuning override
   const int MB = 4 * NT;
   const int auxw = qt == MLXR_Q4_K ? 4 : 8;
   int G = g_num_sms;
   // shared memory left for the x slice when the rings keep at least two stages per warp
-  // two groups need room for 16 rings of at least two stages; otherwise run one group
   auto x_budget = [&](int ng) {
     const int fixed = ng * kSlots * (kGroupWarps + 1) * kTileRows * MB * 4 + 2048 + 256;
     return g_max_smem - 2 * ng * kGroupWarps * kStageBytes - fixed - M * 64 * (auxw + 1) * 4;
   };
+  // Two warp groups per CTA unless one group gets by with fewer K-slices: beyond batch 2 the
+  // activations compete with the rings for shared memory, and a K split over CTAs (a fix-up
+  // through L2 per tile) costs more than the second group gains.
+  int NG = 2;
+  if (force_groups == 1 || force_groups == 2) NG = force_groups;
+  else if (const char* e = getenv("MLXR_DEC_GROUPS")) { const int v = atoi(e); if (v == 1 || v == 2) NG = v; }  // tuning override
+  else if (M > 2) {
+    int worst[3] = {0, 0, 0};
+    for (int ng = 1; ng <= 2; ng++)
+      for (int i = 0; i < nphases; i++) {
+        const DecodeLinear& L = lin[i];
+        int rows = 0;
+        for (int j = 0; j < L.nmat; j++) rows += L.rows[j];
+        const int nt = L.interleave ? (L.rows[0] + 7) / 8 : (rows + kTileRows - 1) / kTileRows;
+        const int sl = choose_slices(nt, L.K / 256, G, ng, M, xrows, x_budget(ng), nphases > 1 || i > 0);
+        worst[ng] = std::max(worst[ng], sl <= 0 ? 1 << 20 : sl);
+      }
+    if (worst[1] < worst[2]) NG = 1;
+  }
   const int max_x = x_budget(NG);
   int max_slice_segs = 0;
   size_t scratch_off = 0;
@@ -205,12 +232,8 @@ int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype
     int S = choose_slices(ph.ntiles, nseg, G, NG, M, xrows, max_x, nphases > 1 || i > 0);
     if (const char* e = getenv("MLXR_DEC_S")) { const int v = atoi(e); if (v >= 1 && v <= nseg && (v & (v - 1)) == 0 && (nphases == 1 || G % v == 0)) S = v; }  // tuning override
     if (S <= 0) {
-      if (NG == 2 && !getenv("MLXR_DEC_GROUPS")) {   // not enough shared memory beside 16 rings: one group
-        setenv("MLXR_DEC_GROUPS", "1", 1);
-        const int rc1 = launch_decode(lin, nphases, M, qt, dtype, scratch, scratch_bytes, sync, bar_host, status, st, tp);
-        unsetenv("MLXR_DEC_GROUPS");
-        return rc1;
-      }
+      if (NG == 2 && force_groups == 0 && !getenv("MLXR_DEC_GROUPS"))   // no room beside 16 rings: one group
+        return launch_decode_impl(lin, nphases, M, qt, dtype, scratch, scratch_bytes, sync, bar_host, status, st, tp, 1);
       set_error("decode kernel: x slice does not fit shared memory (K=%d, M=%d)", L.K, M);
       return MLXR_ERR_UNSUPPORTED;
     }

@@ -50,6 +50,7 @@ struct Params {
   float* partials;    // split-K: [S][M][N] float partial sums (null when S == 1)
   uint32_t* counters; // split-K: one arrival counter per output tile (self-clearing)
   int S;              // K-slices = gridDim.z
+  int vec_loads;      // packed buffer is 16-byte aligned and a multiple of 16 bytes long: vector loads allowed
   int debug;          // tuning probes: 1 skip the conversion math, 2 skip the weight loads
 };
 
@@ -180,17 +181,53 @@ __device__ __forceinline__ uint4 dequant8_bf16(uint32_t v, float ss, float c) {
   return make_uint4(out[0], out[1], out[2], out[3]);
 }
 
+// NW consecutive 32-bit words starting at a 2-byte aligned address, fetched with 16-byte aligned
+// read-only loads and funnel shifts (the 18- and 34-byte blocks never line up with vector loads;
+// one two-byte load per half word would cost 8 to 16 load instructions per thread and stage).
+// Only vectors that contain wanted bytes are read, so the reads stay inside a 16-byte aligned
+// buffer whose size is a multiple of 16.
+template <int NW>
+__device__ __forceinline__ void load_words_2b(const uint8_t* p, uint32_t (&out)[NW]) {
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  const uint4* base = reinterpret_cast<const uint4*>(a & ~(uintptr_t)15);
+  const int off = (int)(a & 15);                    // even
+  constexpr int NV = (14 + NW * 4 - 1) / 16 + 1;    // vectors a worst-case offset can touch
+  uint32_t w[NV * 4 + 1];
+#pragma unroll
+  for (int v = 0; v < NV; v++) {
+    uint4 q = make_uint4(0u, 0u, 0u, 0u);
+    if (v * 16 < off + NW * 4) q = __ldg(base + v);
+    w[4 * v] = q.x; w[4 * v + 1] = q.y; w[4 * v + 2] = q.z; w[4 * v + 3] = q.w;
+  }
+  w[NV * 4] = 0u;
+  const int wo = off >> 2;
+  const uint32_t sh = (uint32_t)(off & 3) * 8u;     // 0 or 16
+#pragma unroll
+  for (int c = 0; c < 4; c++) {
+    if (wo == c) {
+#pragma unroll
+      for (int i = 0; i < NW; i++) out[i] = (c + i + 1 <= NV * 4) ? __funnelshift_r(w[c + i], w[c + i + 1], sh) : 0u;
+    }
+  }
+}
+
 // 32 weights (group hb of k-block kb) of a Q4_0 / Q8_0 / NF4 row -> four 16-byte chunks of the
 // activation dtype.  Blocks of these formats are only 2-byte aligned.  fp16 activations get the
 // reference's value rounded to fp16 (rn16 of the exact product); bf16 one rounding to bf16.
 template <int QT, int BF>
-__device__ __forceinline__ void dequant32_other(const uint8_t* rowp, int kb, int hb, const float* nf4, uint4 (&o)[4]) {
+__device__ __forceinline__ void dequant32_other(const uint8_t* rowp, int kb, int hb, const float* nf4, bool vec, uint4 (&o)[4]) {
   if constexpr (QT == MLXR_Q4_0) {
     const uint8_t* blk = rowp + (size_t)(2 * kb + hb) * 18;          // q_gemm_dequant.metal:142-161
     const __half d = h_from_bits(ld_u16(blk));
+    uint32_t qw[4];
+    if (vec) load_words_2b<4>(blk + 2, qw);
+    else {
+#pragma unroll
+      for (int i = 0; i < 4; i++) qw[i] = (uint32_t)ld_u16(blk + 2 + 4 * i) | ((uint32_t)ld_u16(blk + 4 + 4 * i) << 16);
+    }
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-      const uint32_t v = (uint32_t)ld_u16(blk + 2 + 4 * i) | ((uint32_t)ld_u16(blk + 4 + 4 * i) << 16);
+      const uint32_t v = qw[i];
       if constexpr (BF == 0) o[i] = dequant8_f16(v, __half2half2(d), __half2half2(__ushort_as_half((unsigned short)0)));
       else { const float ss = __half2float(d); o[i] = dequant8_bf16(v, ss, -136.0f * ss); }
     }
@@ -198,13 +235,19 @@ __device__ __forceinline__ void dequant32_other(const uint8_t* rowp, int kb, int
     const uint8_t* blk = rowp + (size_t)(2 * kb + hb) * 34;          // q_gemm_dequant.metal:190-201
     const __half d = h_from_bits(ld_u16(blk));
     const float df = __half2float(d);
+    uint32_t qw[8];
+    if (vec) load_words_2b<8>(blk + 2, qw);
+    else {
+#pragma unroll
+      for (int i = 0; i < 8; i++) qw[i] = (uint32_t)ld_u16(blk + 2 + 4 * i) | ((uint32_t)ld_u16(blk + 4 + 4 * i) << 16);
+    }
 #pragma unroll
     for (int i = 0; i < 4; i++) {
       uint32_t out[4];
 #pragma unroll
       for (int h2 = 0; h2 < 2; h2++) {
         const int wi = 2 * i + h2;
-        const uint32_t u = ((uint32_t)ld_u16(blk + 2 + 4 * wi) | ((uint32_t)ld_u16(blk + 4 + 4 * wi) << 16)) ^ 0x80808080u;  // bytes q + 128
+        const uint32_t u = qw[wi] ^ 0x80808080u;  // bytes q + 128
 #pragma unroll
         for (int j = 0; j < 2; j++) {
           if constexpr (BF == 0) {
@@ -229,9 +272,15 @@ __device__ __forceinline__ void dequant32_other(const uint8_t* rowp, int kb, int
   } else {   // NF4: 64-element blocks of 34 bytes (fp16 absmax, 32 index bytes, low nibble = even element)
     const uint8_t* blk = rowp + (size_t)kb * 34;
     const float am = __half2float(h_from_bits(ld_u16(blk)));
+    uint32_t qw[4];
+    if (vec) load_words_2b<4>(blk + 2 + 16 * hb, qw);
+    else {
+#pragma unroll
+      for (int i = 0; i < 4; i++) qw[i] = (uint32_t)ld_u16(blk + 2 + 16 * hb + 4 * i) | ((uint32_t)ld_u16(blk + 4 + 16 * hb + 4 * i) << 16);
+    }
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-      const uint32_t v = (uint32_t)ld_u16(blk + 2 + 16 * hb + 4 * i) | ((uint32_t)ld_u16(blk + 4 + 16 * hb + 4 * i) << 16);
+      const uint32_t v = qw[i];
       uint32_t out[4];
 #pragma unroll
       for (int j = 0; j < 4; j++) {
@@ -393,7 +442,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
 #pragma unroll
         for (int i = 0; i < 4; i++) o[i] = cq;
       } else if (live && QT != MLXR_Q4_K) {
-        dequant32_other<QT, BF>(rowp, kb, hb, sh->nf4, o);
+        dequant32_other<QT, BF>(rowp, kb, hb, sh->nf4, P.vec_loads != 0, o);
       } else if (live) {
         // header: d, dmin (fp16), scales[12].  scales[3g .. 3g+2] of group g = (kb & 3) >> 1 as
         // one 24-bit value (only scales[0..5] are read); sub-block offset o = (2 (kb & 3) + hb) & 3:
@@ -610,6 +659,7 @@ int launch_prefill(const void* x, const void* w, const void* bias, void* y, int 
   P.partials = S > 1 ? partials : nullptr;
   P.counters = counters;
   P.S = S;
+  P.vec_loads = ((((uintptr_t)w) & 15u) == 0 && ((size_t)N * P.row_bytes) % 16 == 0) ? 1 : 0;
   P.debug = 0;
   if (const char* e = getenv("MLXR_TC_DEBUG")) P.debug = atoi(e);   // tuning probe
   const bool two = M > prefill::kBM;      // a second accumulator only pays when there are rows for it

@@ -151,6 +151,31 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def swiglu_mlp(input: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor,
+               bias_gate: Optional[torch.Tensor] = None, bias_up: Optional[torch.Tensor] = None,
+               bias_down: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """swiglu_mlp(), swiglu_mlp_primitive.h:169-176 / .mm:236-304: dense weights of the activation
+    dtype, w_gate and w_up [inter, hidden], w_down [hidden, inter], optional biases."""
+    if input.dim() != 2:
+        raise _capi.MlxrInvalidArgument(_capi.ERR_INVALID_ARGUMENT, "Input must be 2D [M, hidden_size]")
+    M, hidden = input.shape
+    if w_gate.dim() != 2 or w_gate.shape[1] != hidden or w_up.shape != w_gate.shape:
+        raise _capi.MlxrInvalidArgument(_capi.ERR_INVALID_ARGUMENT, "w_gate and w_up must be [intermediate_size, hidden_size]")
+    inter = w_gate.shape[0]
+    if tuple(w_down.shape) != (hidden, inter):
+        raise _capi.MlxrInvalidArgument(_capi.ERR_INVALID_ARGUMENT, "w_down must be [hidden_size, intermediate_size]")
+    for name, t in (("w_gate", w_gate), ("w_up", w_up), ("w_down", w_down), ("bias_gate", bias_gate),
+                    ("bias_up", bias_up), ("bias_down", bias_down)):
+        if t is not None and t.dtype != input.dtype:
+            raise _capi.MlxrInvalidArgument(_capi.ERR_INVALID_ARGUMENT, f"{name} must have the input's dtype")
+    y = torch.empty_like(input)
+    check(lib.mlxr_mlp_block_dense(_dev(input, "input"), _dev(w_gate, "w_gate"), _dev(w_up, "w_up"),
+                                   _dev(w_down, "w_down"), _dev(bias_gate, "bias_gate"), _dev(bias_up, "bias_up"),
+                                   _dev(bias_down, "bias_down"), y.data_ptr(), M, hidden, inter,
+                                   _dtype_code(input), _stream()))
+    return y
+
+
 def rope_apply(input: torch.Tensor, cos_table: torch.Tensor, sin_table: torch.Tensor,
                positions: torch.Tensor, scaling_mode: RoPEScalingMode = RoPEScalingMode.BASE,
                scale_factor: float = 1.0, position_offset: int = 0, inplace: bool = False,

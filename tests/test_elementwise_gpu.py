@@ -149,3 +149,23 @@ def test_rope_errors():
         mx.rope_apply(x, cos, sin, torch.tensor([0, 16], dtype=torch.int32, device="cuda"))
     with pytest.raises(MlxrError, match="3D"):
         mx.rope_apply(x[0], cos, sin, torch.zeros(2, dtype=torch.int32, device="cuda"))
+
+
+def test_swiglu_mlp_dense_matches_composition():
+    """swiglu_mlp() with dense weights and biases (swiglu_mlp_primitive.mm:47-82) against the
+    same chain in float64."""
+    import mlxr_b200 as mx
+    g = torch.Generator().manual_seed(5)
+    M, H, I = 3, 96, 224
+    x = torch.randn(M, H, generator=g)
+    wg, wu, wd = (torch.randn(I, H, generator=g) * 0.1, torch.randn(I, H, generator=g) * 0.1,
+                  torch.randn(H, I, generator=g) * 0.1)
+    bg, bu, bd = torch.randn(I, generator=g) * 0.1, torch.randn(I, generator=g) * 0.1, torch.randn(H, generator=g) * 0.1
+    y = mx.swiglu_mlp(x.cuda(), wg.cuda(), wu.cuda(), wd.cuda(), bg.cuda(), bu.cuda(), bd.cuda()).cpu().double()
+    xd = x.double()
+    gt = xd @ wg.double().T + bg.double()
+    ut = xd @ wu.double().T + bu.double()
+    want = (gt * torch.sigmoid(gt) * ut) @ wd.double().T + bd.double()
+    assert float((y - want).norm() / want.norm()) < 1e-5
+    with pytest.raises(ValueError):
+        mx.swiglu_mlp(x.cuda(), wg.cuda(), wu.cuda()[:, :8].contiguous(), wd.cuda())
