@@ -18,7 +18,7 @@ def __getattr__(name):
     if name in _OPS:
         from . import ops
         return getattr(ops, name)
-    if name in ("ops", "_capi", "quantize", "build", "build_cpp", "tp"):
+    if name in ("ops", "_capi", "quantize", "build", "build_cpp", "tp", "gguf_layout"):
         import importlib
         return importlib.import_module(f".{name}", __name__)
     raise AttributeError(f"module 'mlxr_b200' has no attribute {name!r}")

@@ -29,8 +29,10 @@
 //              last reduces them in slice order and runs the epilogue
 //   two phases gate/up -> grid barrier -> down in ONE launch: every warp keeps its ring
 //              full with the next phase's weights while the CTA waits at the barrier
-// The only spin wait (grid barrier) is bounded; on expiry a status word is set and the
-// kernel carries on without blocking.
+//   exchange   tensor-parallel block: the last phase stores its fp32 sums into every rank's
+//              exchange buffer (peer stores), raises a flag per CTA and ends with the reduction
+// Every spin wait (mbarrier, slot flag, grid barrier, peer flag) is bounded; on expiry a status
+// word is set and the kernel carries on without blocking.
 #pragma once
 #include <cuda.h>   // CUtensorMap (type only; the encoder is fetched at run time)
 
@@ -176,13 +178,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-// Named barriers 1..15: arrive does not block, sync does; both order shared-memory accesses.
-__device__ __forceinline__ void bar_arrive(int id, int nthreads) {
-  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-__device__ __forceinline__ void bar_sync(int id, int nthreads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 // The MMAs are pure functions of their register operands: not volatile, so the compiler may
 // schedule them among the loads and the logic of neighbouring sub-blocks.
