@@ -521,6 +521,20 @@ int mlxr_q_gemm_dequant_host(const void* x_host, const void* weights_dev, const 
   return MLXR_OK;
 }
 
+// Device-side address of pinned, device-mapped host memory (cudaHostAlloc / cudaHostRegister under
+// unified addressing), or null for anything else.  Asked on every call: an address can change
+// from pinned to pageable between calls.
+static void* mapped_host_pointer(void* p) {
+  cudaPointerAttributes a;
+  void* out = nullptr;
+  if (cudaPointerGetAttributes(&a, p) == cudaSuccess) {
+    if (a.type == cudaMemoryTypeHost && a.devicePointer) out = a.devicePointer;
+  } else {
+    cudaGetLastError();   // pageable memory on old drivers reports an error: not sticky
+  }
+  return out;
+}
+
 int mlxr_mlp_block_host(const void* x_host, const void* norm_weight_dev, const void* w_gate_dev,
                         const void* w_up_dev, const void* w_down_dev, void* y_host, int M, int hidden,
                         int inter, int qt, float eps, int dtype, void* stream) {
@@ -536,10 +550,14 @@ int mlxr_mlp_block_host(const void* x_host, const void* norm_weight_dev, const v
   char* xs = (char*)ws->stage;
   char* ys = xs + xb;
   MLXR_CUDA_TRY(cudaMemcpyAsync(xs, x_host, (size_t)M * hidden * es, cudaMemcpyHostToDevice, st));
-  if (int r = mlxr_mlp_block(xs, norm_weight_dev, w_gate_dev, w_up_dev, w_down_dev, ys, M, hidden, inter,
-                             qt, eps, dtype, stream))
+  // A small result in pinned (device-mapped) host memory is written by the kernel's epilogue
+  // directly - posted stores over PCIe - which saves the copy back; everything else is staged.
+  void* y_direct = nullptr;
+  if ((size_t)M * hidden * es <= 64 * 1024 && !getenv("MLXR_HOST_STAGE_Y")) y_direct = mapped_host_pointer(y_host);
+  if (int r = mlxr_mlp_block(xs, norm_weight_dev, w_gate_dev, w_up_dev, w_down_dev, y_direct ? y_direct : ys, M, hidden,
+                             inter, qt, eps, dtype, stream))
     return r;
-  MLXR_CUDA_TRY(cudaMemcpyAsync(y_host, ys, (size_t)M * hidden * es, cudaMemcpyDeviceToHost, st));
+  if (!y_direct) MLXR_CUDA_TRY(cudaMemcpyAsync(y_host, ys, (size_t)M * hidden * es, cudaMemcpyDeviceToHost, st));
   MLXR_CUDA_TRY(cudaStreamSynchronize(st));
   return MLXR_OK;
 }

@@ -96,6 +96,11 @@ def test_host_buffer_entry_points(oracle):
                                   yh.data_ptr(), M, H, I, qt, 1e-5, 0, st))
     y_dev = mx.mlp_block(xt.cuda(), gam, wg, wu, wd, I, mx.QuantType(qt), 1e-5)
     assert torch.equal(yh, y_dev.cpu())
+    # pageable host memory takes the staged copy instead of the direct stores
+    yp = torch.empty((M, H), dtype=torch.float16)
+    check(lib.mlxr_mlp_block_host(xt.contiguous().data_ptr(), gam.data_ptr(), wg.data_ptr(), wu.data_ptr(), wd.data_ptr(),
+                                  yp.data_ptr(), M, H, I, qt, 1e-5, 0, st))
+    assert torch.equal(yp, y_dev.cpu())
     y2 = torch.empty((M, I), dtype=torch.float16).pin_memory()
     check(lib.mlxr_q_gemm_dequant_host(xh.data_ptr(), wg.data_ptr(), None, y2.data_ptr(), M, I, H, qt, 256, 0, st))
     assert torch.equal(y2, mx.q_gemm_dequant(xt.cuda(), wg, M, I, H, mx.QuantType(qt), 256).cpu())
