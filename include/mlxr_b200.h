@@ -170,7 +170,10 @@ MLXR_API int mlxr_rope_apply(const void* x, const uint16_t* cos_f16, const uint1
  * plan/MetalKernelsPlan.md:109-117 intends.  x, y: [M, hidden]; w_gate, w_up:
  * packed [inter, hidden]; w_down: packed [hidden, inter]; all three in `quant_type`.
  * n and h = SiLU(g)*u are rounded to `dtype` where the composition materialises them;
- * h lives only in this library's workspace (L2-resident at decode sizes). */
+ * h lives only in this library's workspace (L2-resident at decode sizes).  At decode batches
+ * the block is ONE launch: the gate/up CTAs publish h as 8-byte words that carry the launch's
+ * sequence number, and the down-projection CTAs poll those words instead of meeting at a grid
+ * barrier. */
 MLXR_API int mlxr_mlp_block(const void* x, const void* norm_weight, const void* w_gate,
                             const void* w_up, const void* w_down, void* y, int M,
                             int hidden, int inter, int quant_type, float eps, int dtype,
@@ -200,6 +203,14 @@ MLXR_API int mlxr_mlp_block_dense(const void* x, const void* w_gate, const void*
  * call).  The return value is the status of this call itself. */
 MLXR_API int mlxr_stream_status(void* stream, int* status_out);
 
+/* Limit of every device-side wait of this library (copy barriers, hand-over words between the
+ * phases of a persistent kernel, peer flags of the tensor-parallel exchange), in nanoseconds
+ * of the GPU's global timer; process-wide, default 2 s, read at each launch.  A wait that
+ * reaches the limit gives up, the kernel returns, and MLXR_ERR_TIMEOUT is reported through
+ * mlxr_stream_status (the failure-detection design: no wait is unbounded, the context stays
+ * usable).  No counterpart in the reference, whose kernels never wait on one another. */
+MLXR_API int mlxr_set_wait_limit_ns(uint64_t ns);
+
 /* The decode linear (1 <= M <= 8, Q4_K or Q4_0, K a multiple of 256) with NO device allocation,
  * on the first call or later: the kernel's scratch (split-K partial sums, barrier and counter
  * words, status word) is a fixed 4 MiB array inside the loaded module instead of the
@@ -214,12 +225,19 @@ MLXR_API int mlxr_stream_status(void* stream, int* status_out);
  *   - The first call on a device fetches the array's address, zeroes the words that must
  *     start at zero and sets kernel attributes: make it before any stream capture begins.
  *   - A bounded wait that gives up is recorded in the array's own status word, which
- *     mlxr_stream_status does not read.
+ *     mlxr_stream_status does not read: mlxr_static_status reads and clears it.
+ *   - The array is part of the module image: it takes its 4 MiB when the CUDA module is loaded
+ *     (at the latest on the first launch or symbol lookup of this library), not at a call.  A
+ *     host that hands all free memory to its own pool should touch this library first.
  * Same arithmetic and the same results as mlxr_q_gemm_dequant for these shapes. */
 #define MLXR_STATIC_MAX_N 8192
 MLXR_API int mlxr_q_gemm_dequant_static(const void* x, const void* weights, const void* bias,
                                         void* y, int M, int N, int K, int quant_type, int dtype,
                                         void* stream);
+/* Synchronise `stream`, then report and clear the status word of the static array on the
+ * current device (MLXR_OK or MLXR_ERR_TIMEOUT).  Allocates nothing.  No counterpart in the
+ * reference. */
+MLXR_API int mlxr_static_status(void* stream, int* status_out);
 
 /* How the persistent decode kernel is launched (process-wide; no counterpart in the
  * reference, whose Metal command buffers serialise kernels).
@@ -227,10 +245,13 @@ MLXR_API int mlxr_q_gemm_dequant_static(const void* x, const void* weights, cons
  *     serialization.  The kernel starts its weight copies while the previous kernel of the
  *     stream drains and waits (griddepcontrol.wait) before it reads activations.  Contract:
  *     weight buffers are model constants - no kernel still in flight on the stream writes
- *     them - and at most one decode launch runs on a device at a time (two concurrent
- *     streams could each hold part of the SMs at the grid barrier; the bounded wait then
- *     reports MLXR_ERR_TIMEOUT through mlxr_stream_status).
- *   MLXR_DECODE_LAUNCH_COOPERATIVE: cooperative launch, no overlap, no contract. */
+ *     them - and at most one decode launch runs on a device at a time.  The MLP block's
+ *     down-projection CTAs wait for words written by the gate/up CTAs of the same launch; the
+ *     library checks once per device that one CTA per SM is resident, but two decode launches
+ *     on concurrent streams could each hold part of the SMs, in which case the bounded wait
+ *     reports MLXR_ERR_TIMEOUT through mlxr_stream_status.
+ *   MLXR_DECODE_LAUNCH_COOPERATIVE: cooperative launch (the driver guarantees co-residency
+ *     or refuses the launch), no overlap with the previous kernel, no contract. */
 enum { MLXR_DECODE_LAUNCH_COOPERATIVE = 0, MLXR_DECODE_LAUNCH_OVERLAPPED = 2 };
 MLXR_API int mlxr_set_decode_launch_mode(int mode);
 

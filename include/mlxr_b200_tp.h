@@ -46,7 +46,11 @@ MLXR_API int mlxr_tp_unique_id(void* id128);
 /* Collective over all ranks: create the context of `rank` of `world` on the current CUDA
  * device.  Initialises the NCCL communicator, allocates the exchange buffer and maps the
  * peers' buffers (CUDA IPC; all ranks must be processes on one node with peer access).
- * use_peer = 0 skips the exchange buffer (NCCL modes only). */
+ * use_peer = 0 skips the exchange buffer (NCCL modes only).
+ * The outcome is collective too: a rank whose local step fails (an allocation, an IPC mapping)
+ * still joins every collective of the set-up, the ranks agree on the result, and either all
+ * return MLXR_OK or all return an error with nothing left allocated.  mlxr_tp_destroy is
+ * collective as well: every rank calls it at the same point. */
 MLXR_API int mlxr_tp_create(const void* id128, int rank, int world, int use_peer, mlxr_tp_ctx** out);
 MLXR_API int mlxr_tp_destroy(mlxr_tp_ctx* ctx);
 MLXR_API int mlxr_tp_rank(const mlxr_tp_ctx* ctx);
@@ -74,6 +78,22 @@ MLXR_API int mlxr_tp_mlp_block(mlxr_tp_ctx* ctx, const void* x, const void* norm
  * exchange step of mlxr_tp_mlp_block on its own (row-parallel linears outside the MLP). */
 MLXR_API int mlxr_tp_all_reduce(mlxr_tp_ctx* ctx, const float* partial, void* y, size_t n, int dtype,
                                 int exchange, void* stream);
+
+/* The one-shot exchange over exchange buffers the CALLER provides (a host that manages its own
+ * symmetric memory, or a test that plays the peers): buffers[r] is rank r's buffer as mapped in
+ * this process, each mlxr_tp_exchange_buffer_bytes() long, 16-byte aligned, flags zeroed once;
+ * ctl: two zero-initialised uint32 of this rank (sequence number, CTAs finished).  Layout of a
+ * buffer: uint32 flags[8][1024] (source rank, CTA) in the first 64 KB, then float
+ * slots[2][8][MLXR_TP_PEER_MAX_ELEMS] (parity of the call's sequence number, source rank).  Call k
+ * (k = 1, 2, ...) of a rank stores its partial into slot [k & 1][rank] of every buffer, sets
+ * flags[rank][b] = k there for each of its ceil(n / 1024) (at most 256) CTAs b, waits until
+ * flags[r][b] >= k in its own buffer for every r, and adds the slots in rank order.  A wait
+ * that reaches the limit of mlxr_set_wait_limit_ns leaves y unwritten for that CTA's elements
+ * and reports MLXR_ERR_TIMEOUT through mlxr_stream_status(stream); the sequence number still
+ * advances, so the next call is well-formed. */
+MLXR_API size_t mlxr_tp_exchange_buffer_bytes(void);
+MLXR_API int mlxr_tp_all_reduce_buffers(const float* partial, void* y, size_t n, int dtype, int rank,
+                                        int world, void* const* buffers, uint32_t* ctl, void* stream);
 
 #ifdef __cplusplus
 }

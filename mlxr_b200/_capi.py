@@ -44,6 +44,8 @@ PROTOTYPES = {
     "mlxr_mlp_block_partial_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp]),
     "mlxr_mlp_block_dense": (_i, [_vp] * 8 + [_i, _i, _i, _i, _vp]),
     "mlxr_stream_status": (_i, [_vp, _vp]),
+    "mlxr_set_wait_limit_ns": (_i, [C.c_uint64]),
+    "mlxr_static_status": (_i, [_vp, _vp]),
     "mlxr_debug_set_trace_buffer": (_i, [_vp]),
     "mlxr_set_decode_launch_mode": (_i, [_i]),
     "mlxr_q_gemm_dequant_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
@@ -64,6 +66,8 @@ TP_PROTOTYPES = {
     "mlxr_tp_pack_shard": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i]),
     "mlxr_tp_mlp_block": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i, _vp]),
     "mlxr_tp_all_reduce": (_i, [_vp, _vp, _vp, _sz, _i, _i, _vp]),
+    "mlxr_tp_exchange_buffer_bytes": (_sz, []),
+    "mlxr_tp_all_reduce_buffers": (_i, [_vp, _vp, _sz, _i, _i, _i, _vp, _vp, _vp]),
 }
 
 for _name, (_res, _args) in list(PROTOTYPES.items()) + list(TP_PROTOTYPES.items()):

@@ -44,7 +44,7 @@ def _nvcc() -> str:
 def _deps_mtime() -> float:
     """Newest mtime over headers every object depends on."""
     t = 0.0
-    for d in (CSRC, os.path.join(ROOT, "include"), os.path.join(ROOT, "oracle")):
+    for d in (CSRC, os.path.join(ROOT, "include")):
         for f in os.listdir(d):
             if f.endswith((".h", ".cuh", ".inc")):
                 t = max(t, os.path.getmtime(os.path.join(d, f)))
@@ -58,6 +58,15 @@ def sources() -> list[str]:
 def build(force: bool = False, verbose: bool = False) -> str:
     os.makedirs(OBJ, exist_ok=True)
     nvcc = _nvcc()
+    # MLXR_TUNING=1 in the environment keeps the tuning probes (environment overrides read by the
+    # launchers); the default build has none.  A change of flags rebuilds everything.
+    flags = list(NVCC_FLAGS) + (["-DMLXR_TUNING"] if os.environ.get("MLXR_TUNING") == "1" else [])
+    stamp = os.path.join(OBJ, "flags.txt")
+    old = open(stamp).read() if os.path.exists(stamp) else None
+    if old != " ".join(flags):
+        force = True
+        with open(stamp, "w") as f:
+            f.write(" ".join(flags))
     hdr_t = _deps_mtime()
     jobs = []
     objs = []
@@ -70,7 +79,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
     def compile_one(job):
         s, o = job
-        cmd = [nvcc, *NVCC_FLAGS, "-c", s, "-o", o]
+        cmd = [nvcc, *flags, "-c", s, "-o", o]
         p = subprocess.run(cmd, capture_output=True, text=True)
         return s, p.returncode, p.stdout + p.stderr
 

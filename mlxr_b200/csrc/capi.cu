@@ -44,6 +44,8 @@ struct Workspace {
   size_t stage_bytes = 0;
   void* part = nullptr;      // split-K partial sums of the tensor-core GEMM (never aliases buf)
   size_t part_bytes = 0;
+  void* tagged = nullptr;    // h of the decode MLP block as {payload, sequence number} words; zero-filled when
+  size_t tagged_bytes = 0;   // allocated and written by nothing else, so a stale word never carries a live number
   uint32_t* sync = nullptr;  // kSyncWords zero-initialised words (counters, barriers)
   int* status = nullptr;     // device status word
   int* status_host = nullptr;  // pinned mirror
@@ -52,7 +54,7 @@ struct Workspace {
 static std::mutex g_ws_mu;
 static std::map<std::pair<int, void*>, Workspace> g_ws;
 
-static int grow(void** p, size_t* have, size_t need, cudaStream_t st) {
+static int grow(void** p, size_t* have, size_t need, cudaStream_t st, bool zero = false) {
   if (need <= *have) return MLXR_OK;
   // wait for work that may still use the old buffer, then replace it
   MLXR_CUDA_TRY(cudaStreamSynchronize(st));
@@ -62,10 +64,11 @@ static int grow(void** p, size_t* have, size_t need, cudaStream_t st) {
   const size_t cap = (need + ((size_t)1 << 20) - 1) & ~(((size_t)1 << 20) - 1);
   MLXR_CUDA_TRY(cudaMalloc(p, cap));
   *have = cap;
+  if (zero) MLXR_CUDA_TRY(cudaMemsetAsync(*p, 0, cap, st));
   return MLXR_OK;
 }
 
-int get_workspace(cudaStream_t st, size_t need, Workspace** out, size_t need_stage = 0) {
+int get_workspace(cudaStream_t st, size_t need, Workspace** out, size_t need_stage = 0, size_t need_tagged = 0) {
   int dev = 0;
   MLXR_CUDA_TRY(cudaGetDevice(&dev));
   std::lock_guard<std::mutex> lk(g_ws_mu);
@@ -80,6 +83,7 @@ int get_workspace(cudaStream_t st, size_t need, Workspace** out, size_t need_sta
   }
   if (int r = grow(&ws.buf, &ws.bytes, need, st)) return r;
   if (int r = grow(&ws.stage, &ws.stage_bytes, need_stage, st)) return r;
+  if (int r = grow(&ws.tagged, &ws.tagged_bytes, need_tagged, st, true)) return r;
   *out = &ws;
   return MLXR_OK;
 }
@@ -131,6 +135,14 @@ static int check_quant(int qt, int K, int group_size, bool check_group) {
 // split-K partial sums; intermediates of the fused entry points start after them.
 static int run_linear(const void* x, const void* w, const void* bias, void* y, int M, int N, int K,
                       int qt, int dtype, cudaStream_t st) {
+  if (M > 0 && N > 0 && stream_gemv_supported(qt, M, K, &w, 1) && !tune_env("MLXR_NO_STREAM")) {
+    Workspace* ws = nullptr;
+    if (int r = get_workspace(st, 0, &ws)) return r;
+    DecodeLinear L;
+    memset(&L, 0, sizeof(L));
+    L.w[0] = w; L.rows[0] = N; L.nmat = 1; L.K = K; L.x = x; L.y[0] = y; L.bias[0] = bias;
+    return launch_stream_gemv(L, M, dtype, ws->status, st);
+  }
   if (M > 0 && N > 0 && decode_supported(qt, M, K, &w, 1)) {
     Workspace* ws = nullptr;
     if (int r = get_workspace(st, kDecodeScratchBytes, &ws)) return r;
@@ -139,9 +151,9 @@ static int run_linear(const void* x, const void* w, const void* bias, void* y, i
     L.w[0] = w; L.rows[0] = N; L.nmat = 1; L.K = K; L.x = x; L.y[0] = y; L.bias[0] = bias;
     return launch_decode(&L, 1, M, qt, dtype, ws->buf, kDecodeScratchBytes, ws->sync, &ws->bar_host, ws->status, st);
   }
-  if (M > 0 && N > 0 && gemv_rows_supported(qt, M, K, x, w) && !getenv("MLXR_NO_GEMV"))
+  if (M > 0 && N > 0 && gemv_rows_supported(qt, M, K, x, w) && !tune_env("MLXR_NO_GEMV"))
     return launch_gemv_rows(x, w, bias, y, M, N, K, qt, dtype, st);
-  if (M > 0 && N > 0 && prefill_supported(qt, M, N, K, dtype, x, w, y) && !getenv("MLXR_NO_TC")) {
+  if (M > 0 && N > 0 && prefill_supported(qt, M, N, K, dtype, x, w, y) && !tune_env("MLXR_NO_TC")) {
     const int S = prefill_slices(M, N, K);
     Workspace* ws = nullptr;
     if (int r = get_workspace(st, 0, &ws)) return r;
@@ -159,15 +171,14 @@ int mlp_block_tp_fused(const void* x, const void* norm_weight, const void* w_gat
   const void* wgu[2] = {w_gate, w_up};
   if (M < 1 || !decode_supported(qt, M, hidden, wgu, 2) || !decode_supported(qt, M, inter, &w_down, 1)) return MLXR_ERR_UNSUPPORTED;
   Workspace* ws = nullptr;
-  const size_t i_bytes = align_up((size_t)M * inter * dtype_size(dtype), 256);
-  if (int r = get_workspace(st, kDecodeScratchBytes + i_bytes, &ws)) return r;
-  char* base = (char*)ws->buf + kDecodeScratchBytes;
+  if (int r = get_workspace(st, kDecodeScratchBytes, &ws, 0, decode_tagged_bytes(M, inter, dtype))) return r;
   DecodeLinear L[2];
   memset(L, 0, sizeof(L));
   L[0].w[0] = w_gate; L[0].w[1] = w_up; L[0].rows[0] = L[0].rows[1] = inter; L[0].nmat = 2;
   L[0].interleave = 1; L[0].K = hidden; L[0].x = x; L[0].gamma = norm_weight; L[0].eps = eps;
-  L[0].y[0] = base;
-  L[1].w[0] = w_down; L[1].rows[0] = hidden; L[1].nmat = 1; L[1].K = inter; L[1].x = base; L[1].y[0] = tp->y;
+  L[0].y_tagged = ws->tagged;
+  L[1].w[0] = w_down; L[1].rows[0] = hidden; L[1].nmat = 1; L[1].K = inter; L[1].x = ws->tagged; L[1].x_tagged = 1;
+  L[1].y[0] = tp->y;
   L[1].epi[0] = 3;
   return launch_decode(L, 2, M, qt, dtype, ws->buf, kDecodeScratchBytes, ws->sync, &ws->bar_host, ws->status, st, tp);
 }
@@ -359,17 +370,22 @@ static int mlp_block_impl(const void* x, const void* norm_weight, const void* w_
   const size_t n_bytes = align_up((size_t)M * hidden * es, 256);
   const size_t i_bytes = align_up((size_t)M * inter * es, 256);
   Workspace* ws = nullptr;
-  if (int r = get_workspace(st, kDecodeScratchBytes + n_bytes + 2 * i_bytes, &ws)) return r;
-  char* base = (char*)ws->buf + kDecodeScratchBytes;
   const void* wgu[2] = {w_gate, w_up};
-  if (decode_supported(qt, M, hidden, wgu, 2) && decode_supported(qt, M, inter, &w_down, 1)) {
-    // one persistent launch: [RMSNorm ->] gate/up -> SiLU*up -> grid barrier -> down
+  const bool decode = decode_supported(qt, M, hidden, wgu, 2) && decode_supported(qt, M, inter, &w_down, 1);
+  if (int r = get_workspace(st, decode ? kDecodeScratchBytes : kDecodeScratchBytes + n_bytes + 2 * i_bytes, &ws, 0,
+                            decode ? decode_tagged_bytes(M, inter, dtype) : 0))
+    return r;
+  char* base = (char*)ws->buf + kDecodeScratchBytes;
+  if (decode) {
+    // one persistent launch: [RMSNorm ->] gate/up -> SiLU*up -> down; h [M, inter] passes between the
+    // phases through L2 as tagged words (no grid barrier)
     DecodeLinear L[2];
     memset(L, 0, sizeof(L));
     L[0].w[0] = w_gate; L[0].w[1] = w_up; L[0].rows[0] = L[0].rows[1] = inter; L[0].nmat = 2;
     L[0].interleave = 1; L[0].K = hidden; L[0].x = x; L[0].gamma = norm_weight; L[0].eps = eps;
-    L[0].y[0] = base;  // h [M, inter], lives in L2 between the phases
-    L[1].w[0] = w_down; L[1].rows[0] = hidden; L[1].nmat = 1; L[1].K = inter; L[1].x = base; L[1].y[0] = y;
+    L[0].y_tagged = ws->tagged;
+    L[1].w[0] = w_down; L[1].rows[0] = hidden; L[1].nmat = 1; L[1].K = inter; L[1].x = ws->tagged; L[1].x_tagged = 1;
+    L[1].y[0] = y;
     if (y_f32) L[1].epi[0] = 3;
     return launch_decode(L, 2, M, qt, dtype, ws->buf, kDecodeScratchBytes, ws->sync, &ws->bar_host, ws->status, st);
   }
@@ -431,6 +447,12 @@ int mlxr_set_decode_launch_mode(int mode) {
   return MLXR_OK;
 }
 
+int mlxr_set_wait_limit_ns(uint64_t ns) {
+  if (ns == 0) { set_error("mlxr_set_wait_limit_ns: the limit must be positive"); return MLXR_ERR_INVALID_ARGUMENT; }
+  set_wait_limit_ns(ns);
+  return MLXR_OK;
+}
+
 int mlxr_debug_set_trace_buffer(void* dev_ptr) {
   set_decode_trace(dev_ptr);
   return MLXR_OK;
@@ -467,6 +489,18 @@ int mlxr_qkv_rope(const void* x, const void* norm_weight, const void* wq, const 
   Workspace* ws = nullptr;
   if (int r = get_workspace(st, kDecodeScratchBytes + align_up((size_t)M * hidden * es, 256), &ws)) return r;
   const void* wqkv[3] = {wq, wk, wv};
+  if (stream_gemv_supported(qt, M, hidden, wqkv, 3) && !tune_env("MLXR_NO_STREAM")) {
+    DecodeLinear L;
+    memset(&L, 0, sizeof(L));
+    L.w[0] = wq; L.w[1] = wk; L.w[2] = wv;
+    L.rows[0] = q_heads * head_dim; L.rows[1] = L.rows[2] = kv_heads * head_dim; L.nmat = 3;
+    L.K = hidden; L.x = x; L.gamma = norm_weight; L.eps = eps;
+    L.y[0] = q_out; L.y[1] = k_out; L.y[2] = v_out;
+    L.epi[0] = L.epi[1] = 2;
+    L.cos_t = cos_f16; L.sin_t = sin_f16; L.positions = positions;
+    L.head_dim = head_dim; L.max_seq = max_seq_len; L.pos_offset = position_offset;
+    return launch_stream_gemv(L, M, dtype, ws->status, st);
+  }
   if (decode_supported(qt, M, hidden, wqkv, 3)) {
     // one launch: [RMSNorm ->] q, k, v stacked along N, RoPE in the epilogue of q and k rows
     DecodeLinear L;
@@ -553,7 +587,7 @@ int mlxr_mlp_block_host(const void* x_host, const void* norm_weight_dev, const v
   // A small result in pinned (device-mapped) host memory is written by the kernel's epilogue
   // directly - posted stores over PCIe - which saves the copy back; everything else is staged.
   void* y_direct = nullptr;
-  if ((size_t)M * hidden * es <= 64 * 1024 && !getenv("MLXR_HOST_STAGE_Y")) y_direct = mapped_host_pointer(y_host);
+  if ((size_t)M * hidden * es <= 64 * 1024 && !tune_env("MLXR_HOST_STAGE_Y")) y_direct = mapped_host_pointer(y_host);
   if (int r = mlxr_mlp_block(xs, norm_weight_dev, w_gate_dev, w_up_dev, w_down_dev, y_direct ? y_direct : ys, M, hidden,
                              inter, qt, eps, dtype, stream))
     return r;
@@ -573,6 +607,7 @@ int mlxr_release_workspaces(void) {
     if (ws.buf && (e = cudaFree(ws.buf)) != cudaSuccess && first == cudaSuccess) first = e;
     if (ws.stage && (e = cudaFree(ws.stage)) != cudaSuccess && first == cudaSuccess) first = e;
     if (ws.part && (e = cudaFree(ws.part)) != cudaSuccess && first == cudaSuccess) first = e;
+    if (ws.tagged && (e = cudaFree(ws.tagged)) != cudaSuccess && first == cudaSuccess) first = e;
     if (ws.sync && (e = cudaFree(ws.sync)) != cudaSuccess && first == cudaSuccess) first = e;
     if (ws.status && (e = cudaFree(ws.status)) != cudaSuccess && first == cudaSuccess) first = e;
     if (ws.status_host) cudaFreeHost(ws.status_host);

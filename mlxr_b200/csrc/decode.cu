@@ -1,6 +1,7 @@
 // Host side of the persistent decode kernel (decode_kernel.cuh): work planning
 // (K-slices, grid, shared-memory budget) and launch.
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 #include <map>
@@ -16,10 +17,17 @@ using namespace decode;
 
 static unsigned long long* g_trace = nullptr;  // set by mlxr_debug_set_trace_buffer
 void set_decode_trace(void* p) { g_trace = (unsigned long long*)p; }
-static int g_launch_mode = MLXR_DECODE_LAUNCH_OVERLAPPED;
-void set_decode_launch_mode(int mode) { g_launch_mode = mode; }
-static int g_num_sms = 0;
-static int g_max_smem = 0;
+void* get_decode_trace() { return g_trace; }
+static std::atomic<int> g_launch_mode{MLXR_DECODE_LAUNCH_OVERLAPPED};
+void set_decode_launch_mode(int mode) { g_launch_mode.store(mode); }
+static std::atomic<unsigned long long> g_wait_ns{2000000000ull};   // limit of every device-side wait
+void set_wait_limit_ns(unsigned long long ns) { g_wait_ns.store(ns ? ns : 1ull); }
+unsigned long long wait_limit_ns() { return g_wait_ns.load(); }
+
+// Device properties, per device (a process may drive several GPUs).
+struct DevProps { int num_sms = 0; int max_smem = 0; };
+static std::mutex g_props_mu;
+static DevProps g_props[64];
 
 // ---- tensor maps -----------------------------------------------------------------------------
 // A packed matrix [rows][row_bytes] is described to the TMA unit as a 2-D tensor of 8-byte
@@ -57,12 +65,20 @@ static int weight_tensor_map(const void* w, int rows, int row_bytes, CUtensorMap
   return MLXR_OK;
 }
 
-static int device_props() {
-  if (g_num_sms) return MLXR_OK;
+static int device_props(DevProps* out) {
   int dev = 0;
   MLXR_CUDA_TRY(cudaGetDevice(&dev));
-  MLXR_CUDA_TRY(cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev));
-  MLXR_CUDA_TRY(cudaDeviceGetAttribute(&g_max_smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+  if (dev < 0 || dev >= 64) { set_error("device index %d outside 0..63", dev); return MLXR_ERR_INVALID_ARGUMENT; }
+  std::lock_guard<std::mutex> lk(g_props_mu);
+  DevProps& d = g_props[dev];
+  if (!d.num_sms) {
+    int sms = 0, smem = 0;
+    MLXR_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    MLXR_CUDA_TRY(cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    d.max_smem = smem;
+    d.num_sms = sms;
+  }
+  *out = d;
   return MLXR_OK;
 }
 
@@ -100,20 +116,29 @@ static int choose_slices(int ntiles, int nseg, int G, int ng, int M, int xrows, 
 }
 
 template <int QT, typename T, int NT, int NG, bool PAIRS>
-static int launch_inst(const Params& P, const SmemPlan& plan, int G, bool cooperative, cudaStream_t st) {
+static int launch_inst(const Params& P, const SmemPlan& plan, int G, const DevProps& props, cudaStream_t st) {
   auto kern = decode_kernel<QT, T, NT, NG, PAIRS>;
   constexpr int kThreads = NG * kGroupWarps * 32;
+  // Once per (device, instantiation): raise the shared-memory limit and check that a CTA of the
+  // largest plan is resident on every SM, i.e. that a grid of one CTA per SM is co-resident when
+  // the device runs nothing else (chained phases wait for each other's output).
+  static std::mutex mu;
   static bool attr_done[64] = {};
   int dev = 0;
   MLXR_CUDA_TRY(cudaGetDevice(&dev));
-  if (!attr_done[dev & 63]) {
-    MLXR_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, g_max_smem));
-    attr_done[dev & 63] = true;
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (!attr_done[dev & 63]) {
+      MLXR_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, props.max_smem));
+      int per_sm = 0;
+      MLXR_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, (size_t)props.max_smem));
+      if (per_sm < 1) { set_error("decode kernel: a CTA with %d bytes of shared memory is not resident on this device", props.max_smem); return MLXR_ERR_UNSUPPORTED; }
+      attr_done[dev & 63] = true;
+    }
   }
-  // launch mode (tuning override): 0 cooperative, 1 plain, 2 plain with programmatic overlap
-  int mode = g_launch_mode;
-  (void)cooperative;
-  if (const char* e = getenv("MLXR_DEC_LAUNCH")) mode = atoi(e);
+  // launch mode: 0 cooperative, 1 plain, 2 plain with programmatic overlap
+  int mode = g_launch_mode.load();
+  if (const char* e = tune_env("MLXR_DEC_LAUNCH")) mode = atoi(e);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(G);
   cfg.blockDim = dim3(kThreads);
@@ -146,14 +171,21 @@ int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype
 static int launch_decode_impl(const DecodeLinear* lin, int nphases, int M, int qt, int dtype, void* scratch,
                               size_t scratch_bytes, uint32_t* sync, uint32_t* bar_host, int* status, cudaStream_t st,
                               const DecodeTp* tp, int force_groups) {
-  if (int r = device_props()) return r;
+  DevProps props;
+  if (int r = device_props(&props)) return r;
+  const int g_num_sms = props.num_sms, g_max_smem = props.max_smem;
+  if (nphases > 1 && !(nphases == 2 && lin[0].interleave && lin[0].y_tagged && lin[1].x_tagged && lin[1].x == lin[0].y_tagged && !lin[1].gamma)) {
+    set_error("decode kernel: chained phases need the tagged hand-over buffer between them");
+    return MLXR_ERR_INVALID_ARGUMENT;
+  }
   Params P;
   memset(&P, 0, sizeof(P));
   P.nphases = nphases;
   P.M = M;
-  P.gridbar = sync;
+  P.seq_ctl = nphases > 1 ? sync : nullptr;
+  P.wait_ns = g_wait_ns.load();
   P.flags = 0;
-  if (const char* e = getenv("MLXR_DEC_FLAGS")) P.flags = (uint32_t)atoi(e);   // tuning override
+  if (const char* e = tune_env("MLXR_DEC_FLAGS")) P.flags = (uint32_t)atoi(e);
   P.status = status;
   P.trace = g_trace;
   P.tp_world = 0;
@@ -172,9 +204,9 @@ static int launch_decode_impl(const DecodeLinear* lin, int nphases, int M, int q
   }
   // batch <= 2 with Q4_K: pairs in the MMA columns, one n-tile per batch row
   bool pairs = (qt == MLXR_Q4_K && M <= 2);
-  if (const char* e = getenv("MLXR_DEC_PAIRS")) pairs = pairs && atoi(e) != 0;  // tuning override
+  if (const char* e = tune_env("MLXR_DEC_PAIRS")) pairs = pairs && atoi(e) != 0;
   const int NT = pairs ? M : (M <= 4 ? 1 : 2);
-  const int xrows = pairs ? 8 : 2;
+  const int xrows = 2;
   const int MB = 4 * NT;
   const int auxw = qt == MLXR_Q4_K ? 4 : 8;
   int G = g_num_sms;
@@ -188,7 +220,7 @@ static int launch_decode_impl(const DecodeLinear* lin, int nphases, int M, int q
   // through L2 per tile) costs more than the second group gains.
   int NG = 2;
   if (force_groups == 1 || force_groups == 2) NG = force_groups;
-  else if (const char* e = getenv("MLXR_DEC_GROUPS")) { const int v = atoi(e); if (v == 1 || v == 2) NG = v; }  // tuning override
+  else if (const char* e = tune_env("MLXR_DEC_GROUPS")) { const int v = atoi(e); if (v == 1 || v == 2) NG = v; }
   else if (M > 2) {
     int worst[3] = {0, 0, 0};
     for (int ng = 1; ng <= 2; ng++)
@@ -230,9 +262,9 @@ static int launch_decode_impl(const DecodeLinear* lin, int nphases, int M, int q
     ph.row_bytes = nseg * kSegBytes;
     ph.ntiles = L.interleave ? (ph.n_total + 7) / 8 : (ph.n_total + kTileRows - 1) / kTileRows;
     int S = choose_slices(ph.ntiles, nseg, G, NG, M, xrows, max_x, nphases > 1 || i > 0);
-    if (const char* e = getenv("MLXR_DEC_S")) { const int v = atoi(e); if (v >= 1 && v <= nseg && (v & (v - 1)) == 0 && (nphases == 1 || G % v == 0)) S = v; }  // tuning override
+    if (const char* e = tune_env("MLXR_DEC_S")) { const int v = atoi(e); if (v >= 1 && v <= nseg && (v & (v - 1)) == 0 && (nphases == 1 || G % v == 0)) S = v; }
     if (S <= 0) {
-      if (NG == 2 && force_groups == 0 && !getenv("MLXR_DEC_GROUPS"))   // no room beside 16 rings: one group
+      if (NG == 2 && force_groups == 0 && !tune_env("MLXR_DEC_GROUPS"))   // no room beside 16 rings: one group
         return launch_decode_impl(lin, nphases, M, qt, dtype, scratch, scratch_bytes, sync, bar_host, status, st, tp, 1);
       set_error("decode kernel: x slice does not fit shared memory (K=%d, M=%d)", L.K, M);
       return MLXR_ERR_UNSUPPORTED;
@@ -261,6 +293,11 @@ static int launch_decode_impl(const DecodeLinear* lin, int nphases, int M, int q
     ph.head_dim = L.head_dim;
     ph.max_seq = L.max_seq;
     ph.pos_offset = L.pos_offset;
+    ph.y_tagged = (unsigned long long*)L.y_tagged;
+    ph.x_tagged = L.x_tagged;
+    // second of two chained phases: tile lanes run from the last (CTA, group) pair downwards, so
+    // that the pairs with one tile more in the first phase are the ones left without a tile here
+    ph.reverse = (nphases == 2 && i == 1) ? 1 : 0;
     if (S > 1) {
       const size_t bytes = (size_t)S * ph.ntiles * kTileRows * MB * sizeof(float);
       if (scratch_off + bytes > scratch_bytes) { set_error("decode kernel: split-K scratch too small"); return MLXR_ERR_WORKSPACE; }
@@ -279,19 +316,18 @@ static int launch_decode_impl(const DecodeLinear* lin, int nphases, int M, int q
   }
   // shared-memory plan: as many ring stages per warp as fit
   int stages = kMaxStages;
-  if (const char* e = getenv("MLXR_DEC_STAGES")) { const int v = atoi(e); if (v >= 2 && v <= kMaxStages) stages = v; }  // tuning override
+  if (const char* e = tune_env("MLXR_DEC_STAGES")) { const int v = atoi(e); if (v >= 2 && v <= kMaxStages) stages = v; }
   SmemPlan plan = make_plan(NG, stages, max_slice_segs, M, MB, auxw, pairs ? 1 : 0);
   while (plan.total > g_max_smem && stages > 2) {
     stages--;
     plan = make_plan(NG, stages, max_slice_segs, M, MB, auxw, pairs ? 1 : 0);
   }
   if (plan.total > g_max_smem) { set_error("decode kernel: shared memory plan does not fit"); return MLXR_ERR_UNSUPPORTED; }
-  const bool coop = nphases > 1;
   int rc = MLXR_OK;
 #define INST(QT, T, NTV, NGV)                                                                      \
   do {                                                                                             \
-    if (pairs) { if constexpr (QT == MLXR_Q4_K) rc = launch_inst<QT, T, NTV, NGV, true>(P, plan, G, coop, st); } \
-    else rc = launch_inst<QT, T, NTV, NGV, false>(P, plan, G, coop, st);                            \
+    if (pairs) { if constexpr (QT == MLXR_Q4_K) rc = launch_inst<QT, T, NTV, NGV, true>(P, plan, G, props, st); } \
+    else rc = launch_inst<QT, T, NTV, NGV, false>(P, plan, G, props, st);                            \
   } while (0)
 #define BY_NT(QT, T)                                                                   \
   do {                                                                                 \
@@ -308,7 +344,7 @@ static int launch_decode_impl(const DecodeLinear* lin, int nphases, int M, int q
 #undef BY_T
 #undef BY_NT
 #undef INST
-  if (rc == MLXR_OK && nphases > 1) *bar_host += (uint32_t)G * (uint32_t)(nphases - 1);
+  (void)bar_host;
   return rc;
 }
 

@@ -27,12 +27,15 @@
 //   epilogue   plain (+bias) | SiLU(gate)*up on interleaved gate/up rows | RoPE on q/k rows
 //   split-K    K-slices of different CTAs meet in a global scratch; the CTA that arrives
 //              last reduces them in slice order and runs the epilogue
-//   two phases gate/up -> grid barrier -> down in ONE launch: every warp keeps its ring
-//              full with the next phase's weights while the CTA waits at the barrier
+//   two phases gate/up -> down in ONE launch without a grid barrier: the first phase publishes h
+//              as 8-byte words {payload, launch sequence number}; the second phase's prologue
+//              polls the words it needs, and every warp keeps its ring full with the second
+//              phase's weights meanwhile
 //   exchange   tensor-parallel block: the last phase stores its fp32 sums into every rank's
 //              exchange buffer (peer stores), raises a flag per CTA and ends with the reduction
-// Every spin wait (mbarrier, slot flag, grid barrier, peer flag) is bounded; on expiry a status
-// word is set and the kernel carries on without blocking.
+// Every wait (mbarrier, slot flag, hand-over words, peer flag) is bounded by a time limit read from
+// %globaltimer (Params::wait_ns); on expiry a status word is set and the kernel carries on without
+// blocking.
 #pragma once
 #include <cuda.h>   // CUtensorMap (type only; the encoder is fetched at run time)
 
@@ -50,7 +53,6 @@ constexpr int kRowStride = kStageSegs * kSegBytes;      // 288 B: TMA boxes are 
 constexpr int kStageBytes = kTileRows * kRowStride;     // 4608 = 36 x 128
 constexpr int kSlots = 3;                               // tiles in flight per group
 constexpr int kMaxStages = 6;
-constexpr uint32_t kSpinLimit = 1u << 22;
 
 enum Epilogue { kEpiPlain = 0, kEpiRope = 2, kEpiF32 = 3 };   // kEpiF32: fp32 store (partial sums of a sharded linear)
 
@@ -86,6 +88,12 @@ struct Phase {
   // split-K scratch
   float* partials;       // [S][ntiles][16][MB]
   uint32_t* counters;    // [ntiles], zero between launches
+  // hand-over between chained phases without a grid barrier: every 8-byte word carries its
+  // payload (two 16-bit activations or one float) and the launch's sequence number, so a consumer
+  // that sees the number knows the payload is this launch's (a single store publishes both)
+  unsigned long long* y_tagged;   // interleave epilogue writes h here instead of y[0] (null: plain store)
+  int x_tagged;                   // x points at such words: [M][K / per_word]
+  int reverse;                    // tile lanes are numbered from the last (CTA, group) pair downwards
 };
 
 struct Params {
@@ -94,8 +102,9 @@ struct Params {
   Phase ph[2];
   int nphases;
   int M;
-  uint32_t* gridbar;     // two words: arrival count, generation (self-resetting grid barrier)
+  uint32_t* seq_ctl;     // [0] sequence number of the last complete launch, [1] CTAs finished (null: single phase)
   uint32_t flags;        // bit 0: request x before the weight stream (no overlap with the previous kernel's tail)
+  unsigned long long wait_ns;   // limit of every device-side wait, in nanoseconds of %globaltimer
   int* status;
   unsigned long long* trace;  // optional: 16 globaltimer stamps per CTA (null = off)
   // tensor-parallel exchange fused into the last phase (world <= 1: off)
@@ -121,7 +130,8 @@ struct SmemPlan {
   int off_ring, off_x, off_aux, off_delta, off_slots, off_tile, off_params, off_misc, total;
 };
 // aux words per segment: Q4_K 4 (pair sums hi|lo), Q4_0 8 (4 hi words + 4 lo words)
-// pairs: the batch <= 2 mapping (8 masked x rows per batch); else 2 rows (hi, lo) per batch
+// Two int8 rows (hi, lo) per batch row in both fragment mappings.  pairs: the rows are padded so
+// that hi and lo sit 16 bytes apart modulo 128 (the batch <= 2 mapping reads 16 bytes per thread).
 __host__ __device__ inline SmemPlan make_plan(int ng, int stages, int max_slice_segs, int M, int MB, int aux_per_seg, int pairs) {
   SmemPlan p;
   p.stages = stages;
@@ -130,7 +140,7 @@ __host__ __device__ inline SmemPlan make_plan(int ng, int stages, int max_slice_
   p.seg_stride = max_slice_segs;
   p.off_ring = 0;
   p.off_x = ng * kGroupWarps * stages * kStageBytes;
-  p.off_aux = p.off_x + (pairs ? 8 : 2) * M * p.x_stride;
+  p.off_aux = p.off_x + 2 * M * p.x_stride;
   p.off_delta = p.off_aux + M * p.aux_stride * 4;
   p.off_slots = (p.off_delta + M * p.seg_stride * 4 + 15) & ~15;
   p.off_tile = p.off_slots + ng * kSlots * kGroupWarps * kTileRows * MB * 4;
@@ -167,10 +177,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Every device-side wait goes through here: polls `ready` until it holds or limit_ns nanoseconds
+// have passed (the clock is only read after the first 64 polls failed).  False = gave up.
+template <typename F>
+__device__ __forceinline__ bool bounded_wait(F&& ready, unsigned long long limit_ns) {
+#pragma unroll 1
+  for (int i = 0; i < 64; i++)
+    if (ready()) return true;
+  const unsigned long long t0 = global_ns();
+#pragma unroll 1
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; i++)
+      if (ready()) return true;
+    if (global_ns() - t0 > limit_ns) return false;
+  }
+}
 // Bounded wait: false (and *dead set) when the limit is reached.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* dead) {
-  for (uint32_t i = 0; i < kSpinLimit; i++)
-    if (mbar_try_wait(bar, parity)) return true;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* dead, unsigned long long limit_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  if (bounded_wait([&] { return mbar_try_wait(bar, parity); }, limit_ns)) return true;
   *dead = 1;
   return false;
 }
@@ -222,6 +253,7 @@ __device__ __forceinline__ TileLane tile_lane(const Phase& ph, int cta, int G, i
   TileLane tl;
   tl.step = ph.lane_step;
   tl.first = (cta >> ph.s_shift) * ng + group;
+  if (ph.reverse) tl.first = tl.step - 1 - tl.first;
   // floor((ntiles - 1 - first) / step) + 1 without a division (first < step)
   tl.count = tl.first <= ph.lane_r ? ph.lane_q + 1 : ph.lane_q;
   return tl;
@@ -254,14 +286,14 @@ __device__ __forceinline__ void load8(const T* p, float (&v)[8]) {
 // segment, stored as hi / lo signed bytes in MMA k order, plus the per-segment scale and the
 // per-sub-block sums the offset / min term needs.  One warp per segment, 8 consecutive
 // elements per lane; with a segment per warp the slice is read from L2 exactly once.
-// PAIRS: layout of the batch <= 2 mapping (see segment_mma_pairs): per batch eight rows
-// (pair p, part), row (p, part) holding x only inside the sub-blocks of pair p, and the sums
-// as plain floats.  pre / gpre: x and gamma of (batch 0, segment = warp) loaded by the caller
+// PAIRS: the batch <= 2 mapping (see segment_mma_pairs) shares the layout of x (a hi row and a
+// lo row per batch row) and keeps the pair sums as plain floats.  pre / gpre: x and gamma of (batch 0, segment = warp) loaded by the caller
 // before it queued the weight prefetch (loads issued later wait behind it in the LSU).
 template <int QT, typename T, bool PAIRS>
 __device__ __forceinline__ void x_prologue(const Phase& ph, const SmemPlan& plan, uint8_t* smem, Misc* misc,
                                            int M, int nseg, int seg0, int nwarps, bool have_pre,
-                                           const float (&pre)[8], const float (&gpre)[8], unsigned long long* tr) {
+                                           const float (&pre)[8], const float (&gpre)[8], unsigned long long* tr,
+                                           uint32_t seq, unsigned long long wait_ns) {
   auto tstamp = [&](int i) { if (tr && threadIdx.x == 0) { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); tr[i] = t; } };
   constexpr int AUXW = (QT == MLXR_Q4_K) ? 4 : 8;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -296,17 +328,7 @@ __device__ __forceinline__ void x_prologue(const Phase& ph, const SmemPlan& plan
       else       { hi_e |= hb << (8 * (i >> 1)); lo_e |= lb << (8 * (i >> 1)); }
     }
     // bytes of an 8-group are stored as (e0,e2,e4,e6 | e1,e3,e5,e7): the MMA k order
-    if constexpr (PAIRS) {
-      // sub-block lane/4 belongs to pair {0,1,0,0,2,3,2,2}[lane/4]; the other pairs' rows get zeros
-      const int myp = (0x22320010u >> (4 * (lane >> 2))) & 7;
-      uint8_t* xrow = smem + plan.off_x + (size_t)(8 * m) * plan.x_stride + sg * 256 + lane * 8;
-#pragma unroll
-      for (int p4 = 0; p4 < 4; p4++) {
-        const bool mine = p4 == myp;
-        *reinterpret_cast<uint2*>(xrow + (size_t)(2 * p4) * plan.x_stride) = mine ? make_uint2(hi_e, hi_o) : make_uint2(0u, 0u);
-        *reinterpret_cast<uint2*>(xrow + (size_t)(2 * p4 + 1) * plan.x_stride) = mine ? make_uint2(lo_e, lo_o) : make_uint2(0u, 0u);
-      }
-    } else {
+    {
       uint8_t* xrow = smem + plan.off_x + (size_t)(2 * m) * plan.x_stride + sg * 256 + lane * 8;
       *reinterpret_cast<uint2*>(xrow) = make_uint2(hi_e, hi_o);
       *reinterpret_cast<uint2*>(xrow + plan.x_stride) = make_uint2(lo_e, lo_o);
@@ -340,8 +362,71 @@ __device__ __forceinline__ void x_prologue(const Phase& ph, const SmemPlan& plan
         arow[4 + lane] = pack_half2(__float2half_rn(fa - __half2float(ha)), __float2half_rn(fb - __half2float(hb2)));
       }
     }
-
   };
+  if (ph.x_tagged) {
+    // ---- x is the previous phase's output in tagged words: poll until every word carries this
+    // launch's sequence number (the producer may still be running on another SM), no barrier ----
+    constexpr int PW = sizeof(T) == 2 ? 2 : 1;   // activations per tagged word
+    constexpr int NV = 8 / PW / 2;               // 16-byte loads (two words each) per lane and segment
+    const unsigned long long* xt = reinterpret_cast<const unsigned long long*>(ph.x);
+    const int nitems = M * nseg;
+    auto ld16 = [](const uint4* p) {
+      uint4 r;
+      asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p) : "memory");
+      return r;
+    };
+    for (int base = warp; base < nitems; base += 4 * nwarps) {
+      uint4 raw[4][NV];
+      // request up to four segments before looking at any of them
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int item = base + u * nwarps;
+        if (item < nitems) {
+          const int m = item / nseg, sg = item - m * nseg;
+          const uint4* p = reinterpret_cast<const uint4*>(xt + ((size_t)m * ph.K + k0 + sg * 256 + lane * 8) / PW);
+#pragma unroll
+          for (int q = 0; q < NV; q++) raw[u][q] = ld16(p + q);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int item = base + u * nwarps;
+        if (item >= nitems) break;   // uniform per warp
+        const int m = item / nseg, sg = item - m * nseg;
+        const uint4* p = reinterpret_cast<const uint4*>(xt + ((size_t)m * ph.K + k0 + sg * 256 + lane * 8) / PW);
+        auto tagged = [&] {
+          bool good = true;
+#pragma unroll
+          for (int q = 0; q < NV; q++) good = good && raw[u][q].y == seq && raw[u][q].w == seq;
+          return good;
+        };
+        if (!tagged()) {
+          const bool ok = bounded_wait([&] {
+#pragma unroll
+            for (int q = 0; q < NV; q++) raw[u][q] = ld16(p + q);
+            return tagged();
+          }, wait_ns);
+          if (!ok) misc->dead = 1;
+        }
+        __syncwarp();
+        float v[8];
+#pragma unroll
+        for (int q = 0; q < NV; q++) {
+          if constexpr (PW == 2) {
+            const T* a = reinterpret_cast<const T*>(&raw[u][q].x);
+            const T* b = reinterpret_cast<const T*>(&raw[u][q].z);
+            v[4 * q + 0] = Act<T>::to_f(a[0]); v[4 * q + 1] = Act<T>::to_f(a[1]);
+            v[4 * q + 2] = Act<T>::to_f(b[0]); v[4 * q + 3] = Act<T>::to_f(b[1]);
+          } else {
+            v[2 * q + 0] = __uint_as_float(raw[u][q].x);
+            v[2 * q + 1] = __uint_as_float(raw[u][q].z);
+          }
+        }
+        emit(m, sg, v);
+      }
+    }
+    return;
+  }
   if (M > 2) {
     // ---- batch rows in parallel: (row, segment) items are dealt to the warps round-robin ----
     if (gam) {
@@ -593,35 +678,44 @@ __device__ __forceinline__ void segment_mma(const uint8_t* rl, const uint8_t* rh
 }
 
 // ---- the same for batch <= 2: pairs in the MMA columns (Q4_K) -----------------------------------
-// MMA column 2p + part of n-tile j holds batch j's x restricted to the sub-blocks of (scale, min)
-// pair p (four masked copies of x in shared memory), so one accumulation runs over the whole
-// 256-block with no reset, and thread (g, c) ends up with the hi / lo sums of pair c for rows g
-// and g+8: it scales them with the pair it decoded itself -- no shuffles.  Because the masks
-// live in the data, one MMA may mix sub-blocks: thread c feeds words of sub-block c (then 4+c),
-// which lets weights and x come in 128-bit loads (12 shared loads per segment instead of 29).
+// MMA column 2p + part of n-tile j stands for batch j's x restricted to the sub-blocks of (scale,
+// min) pair p, so one accumulation runs over the whole 256-block with no reset, and thread (g, c)
+// ends up with the hi / lo sums of pair c for rows g and g+8: it scales them with the pair it
+// decoded itself -- no shuffles.  Thread c feeds the words of sub-block c (then 4+c), which lets
+// weights and x come in 128-bit loads.  The restriction costs nothing: a thread's B fragment for
+// column g covers exactly sub-block c (or 4+c), so it is either that sub-block's x bytes or zero,
+// decided by two per-thread constants (keep0 / keep1); x is stored once (hi row, lo row).
+// The two halves of the block accumulate independently (two short MMA chains instead of one).
 // The four threads of a quad hold different pairs' partial sums; the epilogue warp adds them.
-// x0: this lane's x row (g) of batch 0 at the segment, + 32 c; sx0: pair sums of batch 0 at the
-// segment, + c; dl0: delta of batch 0 at the segment.
+// x0: this lane's x row (part g & 1) of batch 0 at the segment, + 32 c; sx0: pair sums of batch 0
+// at the segment, + c; dl0: delta of batch 0 at the segment.
 template <int NT>
 __device__ __forceinline__ void segment_mma_pairs(const uint8_t* rl, const uint8_t* rh, const uint8_t* x0, int x_batch_stride,
                                                   const float* sx0, int aux_stride, const float* dl0, int seg_stride,
-                                                  int c, int sh1, int sh2, float (&total)[NT][2]) {
+                                                  int c, int sh1, int sh2, bool keep0, bool keep1, float (&total)[NT][2]) {
   const uint4 hl = *reinterpret_cast<const uint4*>(rl), hh = *reinterpret_cast<const uint4*>(rh);
   uint4 wl[2], wh[2];
   wl[0] = *reinterpret_cast<const uint4*>(rl + 16 + 16 * c);
   wl[1] = *reinterpret_cast<const uint4*>(rl + 80 + 16 * c);
   wh[0] = *reinterpret_cast<const uint4*>(rh + 16 + 16 * c);
   wh[1] = *reinterpret_cast<const uint4*>(rh + 80 + 16 * c);
-  int acc[NT][4];
+  int acc[2][NT][4];
 #pragma unroll
-  for (int j = 0; j < NT; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0;
+  for (int h = 0; h < 2; h++)
+#pragma unroll
+    for (int j = 0; j < NT; j++) acc[h][j][0] = acc[h][j][1] = acc[h][j][2] = acc[h][j][3] = 0;
 #pragma unroll
   for (int h = 0; h < 2; h++) {
+    const bool keep = h ? keep1 : keep0;
     uint4 xa[NT], xb[NT];
 #pragma unroll
     for (int j = 0; j < NT; j++) {
-      xa[j] = *reinterpret_cast<const uint4*>(x0 + (size_t)j * x_batch_stride + 128 * h);
-      xb[j] = *reinterpret_cast<const uint4*>(x0 + (size_t)j * x_batch_stride + 128 * h + 16);
+      xa[j] = make_uint4(0u, 0u, 0u, 0u);
+      xb[j] = make_uint4(0u, 0u, 0u, 0u);
+      if (keep) {
+        xa[j] = *reinterpret_cast<const uint4*>(x0 + (size_t)j * x_batch_stride + 128 * h);
+        xb[j] = *reinterpret_cast<const uint4*>(x0 + (size_t)j * x_batch_stride + 128 * h + 16);
+      }
     }
     const uint32_t wlw[4] = {wl[h].x, wl[h].y, wl[h].z, wl[h].w}, whw[4] = {wh[h].x, wh[h].y, wh[h].z, wh[h].w};
 #pragma unroll
@@ -632,7 +726,7 @@ __device__ __forceinline__ void segment_mma_pairs(const uint8_t* rl, const uint8
       for (int j = 0; j < NT; j++) {
         const uint32_t b0 = i == 0 ? xa[j].x : i == 1 ? xa[j].z : i == 2 ? xb[j].x : xb[j].z;
         const uint32_t b1 = i == 0 ? xa[j].y : i == 1 ? xa[j].w : i == 2 ? xb[j].y : xb[j].w;
-        imma16832(acc[j], a0, a1, a2, a3, b0, b1);
+        imma16832(acc[h][j], a0, a1, a2, a3, b0, b1);
       }
     }
   }
@@ -650,7 +744,8 @@ __device__ __forceinline__ void segment_mma_pairs(const uint8_t* rl, const uint8
   for (int j = 0; j < NT; j++) {
     const float sx = sx0[(size_t)j * aux_stride];
     const float dl = dl0[(size_t)j * seg_stride];
-    const float v0 = (float)(acc[j][0] * 256 + acc[j][1]), v1 = (float)(acc[j][2] * 256 + acc[j][3]);
+    const float v0 = (float)((acc[0][j][0] + acc[1][j][0]) * 256 + (acc[0][j][1] + acc[1][j][1]));
+    const float v1 = (float)((acc[0][j][2] + acc[1][j][2]) * 256 + (acc[0][j][3] + acc[1][j][3]));
     total[j][0] = fmaf(dl, fmaf(ss_l, v0, of_l * sx), total[j][0]);
     total[j][1] = fmaf(dl, fmaf(ss_h, v1, of_h * sx), total[j][1]);
   }
@@ -660,7 +755,7 @@ __device__ __forceinline__ void segment_mma_pairs(const uint8_t* rl, const uint8
 // tile[row][col] holds the complete sums of this CTA's K-slice for 16 rows x MB batch columns.
 template <typename T, int MB>
 __device__ __forceinline__ void tile_epilogue(const Params& P, const Phase& ph, float* tile, int t, int ks, int lane,
-                                              uint32_t tp_seq) {
+                                              uint32_t tp_seq, uint32_t seq) {
   const int M = P.M;
   bool do_epilogue = true;
   if (ph.S > 1) {
@@ -689,7 +784,37 @@ __device__ __forceinline__ void tile_epilogue(const Params& P, const Phase& ph, 
     }
   }
   if (!do_epilogue) return;
-  if (ph.interleave) {
+  if (ph.interleave && ph.y_tagged) {
+    // the same, published as tagged words {payload, sequence number}: one 8-byte store makes the
+    // values and their validity visible together, so the next phase needs neither fence nor barrier
+    auto hval = [&](int r, int m) {
+      const float gv = Act<T>::to_f(Act<T>::from_f(tile[r * MB + m]));
+      const float uv = Act<T>::to_f(Act<T>::from_f(tile[(r + 8) * MB + m]));
+      return Act<T>::from_f(swish_f(gv) * uv);
+    };
+    if constexpr (sizeof(T) == 2) {
+      for (int e = lane; e < 4 * MB; e += 32) {
+        const int rp = e / MB, m = e % MB;
+        const int col = 8 * t + 2 * rp;
+        if (m < M && col < ph.n_total) {
+          const T h0 = hval(2 * rp, m), h1 = hval(2 * rp + 1, m);
+          const uint32_t payload = (uint32_t)*reinterpret_cast<const uint16_t*>(&h0) | ((uint32_t)*reinterpret_cast<const uint16_t*>(&h1) << 16);
+          const unsigned long long word = (unsigned long long)payload | ((unsigned long long)seq << 32);
+          asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(ph.y_tagged + ((size_t)m * ph.n_total + col) / 2), "l"(word) : "memory");
+        }
+      }
+    } else {
+      for (int e = lane; e < 8 * MB; e += 32) {
+        const int r = e / MB, m = e % MB;
+        const int col = 8 * t + r;
+        if (m < M && col < ph.n_total) {
+          const float h0 = Act<float>::to_f(hval(r, m));
+          const unsigned long long word = (unsigned long long)__float_as_uint(h0) | ((unsigned long long)seq << 32);
+          asm volatile("st.volatile.global.u64 [%0], %1;" ::"l"(ph.y_tagged + (size_t)m * ph.n_total + col), "l"(word) : "memory");
+        }
+      }
+    }
+  } else if (ph.interleave) {
     // rows 0..7 gate, 8..15 up of the same 8 intermediate indices: h = SiLU(g) * u
     for (int e = lane; e < 8 * MB; e += 32) {
       const int r = e / MB, m = e % MB;
@@ -902,6 +1027,10 @@ decode_kernel(const __grid_constant__ Params Pg, const __grid_constant__ SmemPla
   // tensor-parallel exchange: this launch's sequence number (stable: the previous launch is complete)
   uint32_t tp_seq = 0;
   if (P.tp_world > 1) tp_seq = *reinterpret_cast<volatile uint32_t*>(P.tp_ctl) + 1u;
+  // the same for the hand-over between chained phases
+  uint32_t seq = 0;
+  if (P.seq_ctl) seq = *reinterpret_cast<volatile uint32_t*>(P.seq_ctl) + 1u;
+  const unsigned long long wait_ns = P.wait_ns;
   // x (and gamma) of batch 0 for this warp's first segment are requested up front so that
   // their latency overlaps the set-up below
   float pre[8] = {0, 0, 0, 0, 0, 0, 0, 0}, gpre[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -918,46 +1047,30 @@ decode_kernel(const __grid_constant__ Params Pg, const __grid_constant__ SmemPla
   }
   if (x_first) for (int i = 0; i < D; i++) issue();
   const int sh1 = c < 2 ? 12 * c : 24, sh2 = c == 3 ? 12 : 0;   // bit position of (scale, min) pair c
+  // sub-block s belongs to (scale, min) pair {0,1,0,0,2,3,2,2}[s]; this thread's MMA column g stands
+  // for pair g >> 1 and its B fragment covers sub-block c (first half of a block) or 4 + c (second)
+  const bool keep0 = (int)((0x22320010u >> (4 * c)) & 7u) == (g >> 1);
+  const bool keep1 = (int)((0x22320010u >> (4 * (c + 4))) & 7u) == (g >> 1);
 
   int qg = 0;  // sequence number of the tile within this group (indexes the hand-over slots)
 
   for (int phs = 0; phs < P.nphases; phs++) {
     const Phase& ph = P.ph[phs];
     if (phs > 0) {
-      // ---- grid barrier: every CTA has finished (and made visible) the previous phase ----
+      // No grid barrier: the previous phase's output arrives as tagged words that the prologue
+      // below polls.  The CTA barrier only protects this CTA's own x slice in shared memory,
+      // which warps still working on the previous phase are reading.
       if (warp == 0) stamp(8);
       __syncthreads();
       stamp(9);
-      if (tid == 0) {
-        // self-resetting barrier (safe under CUDA-graph replay): word 0 counts arrivals, word 1 is
-        // the generation; the last CTA to arrive clears the count and bumps the generation.
-        // The CTA barrier above orders every thread's stores before this thread's fence.
-        uint32_t gen;
-        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(gen) : "l"(P.gridbar + 1) : "memory");
-        __threadfence();
-        if (atomicAdd(P.gridbar, 1u) == (uint32_t)G - 1u) {
-          atomicExch(P.gridbar, 0u);          // nobody touches the count again before the next launch
-          asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(P.gridbar + 1) : "memory");
-        } else {
-          bool ok = false;
-          for (uint32_t i = 0; i < kSpinLimit; i++) {
-            uint32_t now;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(now) : "l"(P.gridbar + 1) : "memory");
-            if (now != gen) { ok = true; break; }
-          }
-          if (!ok) misc->dead = 1;
-        }
-      }
-      __syncthreads();
-      stamp(10);
     }
-    // group 0 owns the lowest tile of the CTA: no tile there means no work in this phase
-    if (tile_lane(ph, cta, G, 0, NG).count == 0) continue;   // uniform per CTA
+    // no tile for any group of this CTA: no work in this phase (uniform per CTA)
+    if (tile_lane(ph, cta, G, 0, NG).count + tile_lane(ph, cta, G, NG - 1, NG).count == 0) continue;
 
     const int ks = (cta & (ph.S - 1));
     const int nseg = slice_segs(ph, ks), seg0 = slice_seg0(ph, ks);
     x_prologue<QT, T, PAIRS>(ph, plan, smem, misc, M, nseg, seg0, kAllWarps, have_pre && phs == 0, pre, gpre,
-                             (P.trace && phs == 0) ? P.trace + (size_t)cta * 16 : nullptr);
+                             (P.trace && phs == 0) ? P.trace + (size_t)cta * 16 : nullptr, seq, wait_ns);
 
     __syncthreads();
     stamp(1 + 4 * phs);
@@ -974,15 +1087,15 @@ decode_kernel(const __grid_constant__ Params Pg, const __grid_constant__ SmemPla
         for (int ch = 0; ch < nch; ch++) {
           const int csegs = min(kStageSegs, nsw - ch * kStageSegs);
           const uint8_t* st = ring_g + (size_t)st_cons * kStageBytes + rg * kRowStride;
-          mbar_wait(smem_u32(&misc->full[warp][st_cons]), par_cons, &misc->dead);
+          mbar_wait(smem_u32(&misc->full[warp][st_cons]), par_cons, &misc->dead, wait_ns);
           if (it == 0 && ch == 0 && warp == 0) stamp(2 + 4 * phs);
           for (int sl = 0; sl < csegs; sl++) {
             const int sg = s0w + ch * kStageSegs + sl;  // segment index within the slice
             if constexpr (PAIRS) {
               segment_mma_pairs<NT>(st + sl * kSegBytes, st + sl * kSegBytes + 8 * kRowStride,
-                                    smem + plan.off_x + (size_t)g * plan.x_stride + sg * 256 + 32 * c, 8 * plan.x_stride,
+                                    smem + plan.off_x + (size_t)(g & 1) * plan.x_stride + sg * 256 + 32 * c, 2 * plan.x_stride,
                                     reinterpret_cast<const float*>(aux) + sg * 4 + c, plan.aux_stride,
-                                    delta + sg, plan.seg_stride, c, sh1, sh2, total);
+                                    delta + sg, plan.seg_stride, c, sh1, sh2, keep0, keep1, total);
             } else {
               const uint8_t* xb[NT];
               const uint32_t* auxp[NT];
@@ -1008,9 +1121,7 @@ decode_kernel(const __grid_constant__ Params Pg, const __grid_constant__ SmemPla
         // barrier, so that the eight writers do not have to meet (bounded poll)
         {
           volatile int* fr = &misc->slot_free[group][slot];
-          bool ok = false;
-          for (uint32_t i = 0; i < kSpinLimit; i++) if (*fr >= qg) { ok = true; break; }
-          if (!ok) misc->dead = 1;
+          if (!bounded_wait([&] { return *fr >= qg; }, wait_ns)) misc->dead = 1;
         }
         float* mine = slots + ((size_t)slot * kGroupWarps + wg) * kTileRows * MB;
         if constexpr (PAIRS) {
@@ -1068,7 +1179,7 @@ decode_kernel(const __grid_constant__ Params Pg, const __grid_constant__ SmemPla
             __threadfence_block();
             *reinterpret_cast<volatile int*>(&misc->slot_free[group][slot]) = qg + kSlots;
           }
-          tile_epilogue<T, MB>(P, ph, tile, t, ks, lane, tp_seq);
+          tile_epilogue<T, MB>(P, ph, tile, t, ks, lane, tp_seq, seq);
           __syncwarp();
         }
       }
@@ -1109,12 +1220,11 @@ decode_kernel(const __grid_constant__ Params Pg, const __grid_constant__ SmemPla
       bool ok = true;
       if (lane < P.tp_world) {
         const uint32_t* f = tp_flag(mine, lane, per_cta ? cta : t);
-        ok = false;
-        for (uint32_t i = 0; i < kSpinLimit; i++) {
+        ok = bounded_wait([&] {
           uint32_t v;
           asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-          if ((int32_t)(v - tp_seq) >= 0) { ok = true; break; }
-        }
+          return (int32_t)(v - tp_seq) >= 0;
+        }, wait_ns);
       }
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { misc->dead = 1; continue; }
@@ -1132,6 +1242,15 @@ decode_kernel(const __grid_constant__ Params Pg, const __grid_constant__ SmemPla
   }
   __syncthreads();
   if (tid == 0 && misc->dead) atomicExch(P.status, MLXR_ERR_TIMEOUT);
+  if (P.seq_ctl && tid == 0) {
+    // the last CTA to finish publishes this launch's sequence number for the next launch to read
+    __threadfence();
+    if (atomicAdd(P.seq_ctl + 1, 1u) == (uint32_t)G - 1u) {
+      P.seq_ctl[1] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(P.seq_ctl) = seq;
+    }
+  }
   if (P.tp_world > 1 && tid == 0) {
     // the last CTA to finish advances the sequence number for the next launch
     __threadfence();

@@ -3,6 +3,7 @@
 #include <cuda_runtime.h>
 #include <stddef.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace mlxr {
 
@@ -66,9 +67,27 @@ struct DecodeLinear {
   const uint16_t* sin_t;
   const int32_t* positions;
   int head_dim, max_seq, pos_offset;
+  // Hand-over between two chained phases (gate/up -> down) without a grid barrier: the first
+  // phase's SiLU(gate)*up epilogue writes 8-byte words {payload, launch sequence number} to
+  // y_tagged ([M][rows / per_word] words; per_word = 2 for 16-bit activations, 1 for float), the
+  // second phase has x pointing at the same words and x_tagged = 1.
+  void* y_tagged;
+  int x_tagged;
 };
+// Bytes of the tagged hand-over buffer for h [M, inter].
+inline size_t decode_tagged_bytes(int M, int inter, int dtype) { return (size_t)M * inter * (dtype == MLXR_F32 ? 8 : 4); }
+// Limit of every device-side wait (mbarrier, hand-over words, peer flags), in nanoseconds.
+void set_wait_limit_ns(unsigned long long ns);
+unsigned long long wait_limit_ns();
+// Environment probes for tuning exist only in builds with -DMLXR_TUNING.
+#ifdef MLXR_TUNING
+inline const char* tune_env(const char* name) { return getenv(name); }
+#else
+inline const char* tune_env(const char*) { return nullptr; }
+#endif
 constexpr size_t kDecodeScratchBytes = (size_t)8 << 20;  // split-K partial sums
 void set_decode_trace(void* dev_ptr);
+void* get_decode_trace();
 void set_decode_launch_mode(int mode);
 bool decode_supported(int qt, int M, int K, const void* const* w, int nmat);
 // tp (optional): the last phase must be a single plain linear with epi 3 (float partial sums); its
@@ -81,6 +100,17 @@ int launch_decode(const DecodeLinear* lin, int nphases, int M, int qt, int dtype
 int mlp_block_tp_fused(const void* x, const void* norm_weight, const void* w_gate, const void* w_up, const void* w_down,
                        int M, int hidden, int inter_local, int qt, float eps, int dtype, const DecodeTp* tp,
                        cudaStream_t st);
+
+// ---- streaming decode linear for Q4_K at batch 1 and 2 (stream_gemv.cu) ------------------------
+// One launch per linear (or per stacked / interleaved group of linears): many small CTAs, weights
+// straight from global memory into tensor-core fragments, bulk L2 prefetch, programmatic stream
+// serialization between consecutive launches.  Takes the DecodeLinear description (no tagged
+// hand-over: chained linears are separate launches).
+bool stream_gemv_supported(int qt, int M, int K, const void* const* w, int nmat);
+// next_w / next_bytes (optional): packed weights of the launch the caller issues next on the stream; the
+// tail of this launch requests them into L2.
+int launch_stream_gemv(const DecodeLinear& L, int M, int dtype, int* status, cudaStream_t st,
+                       const void* next_w = nullptr, size_t next_bytes = 0);
 
 // ---- tensor-core GEMM for batch >= 9 on Q4_K with 16-bit activations (prefill.cu) -------------
 bool prefill_supported(int qt, int M, int N, int K, int dtype, const void* x, const void* w, const void* y);

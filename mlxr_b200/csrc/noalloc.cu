@@ -94,3 +94,18 @@ extern "C" int mlxr_q_gemm_dequant_static(const void* x, const void* w, const vo
               "%zu bytes; use mlxr_q_gemm_dequant", M, N, K, kStaticPartialBytes);
   return rc;
 }
+
+extern "C" int mlxr_static_status(void* stream, int* status_out) {
+  cudaStream_t st = (cudaStream_t)stream;
+  PerDevice* d = nullptr;
+  if (int r = static_scratch(st, &d)) return r;
+  int* status = reinterpret_cast<int*>(d->base + kStaticPartialBytes + kStaticSyncBytes);
+  int value = 0;
+  // pageable destination: the copy is staged by the driver and complete when the call returns
+  MLXR_CUDA_TRY(cudaMemcpyAsync(&value, status, sizeof(int), cudaMemcpyDeviceToHost, st));
+  MLXR_CUDA_TRY(cudaMemsetAsync(status, 0, sizeof(int), st));
+  MLXR_CUDA_TRY(cudaStreamSynchronize(st));
+  if (status_out) *status_out = value;
+  if (value == MLXR_ERR_TIMEOUT) set_error("a bounded device-side wait expired in an earlier mlxr_q_gemm_dequant_static call on this device");
+  return MLXR_OK;
+}

@@ -417,7 +417,11 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     };
     // nibbles are requested two k-blocks ahead (q0: even, q1: odd steps); the header of a
     // super-block arrives with its first k-block and is copied out before the next one overwrites it
+#ifdef MLXR_TUNING
     const bool loads = live && !(P.debug & 2) && QT == MLXR_Q4_K;
+#else
+    const bool loads = live && QT == MLXR_Q4_K;
+#endif
     uint4 ch = make_uint4(0, 0, 0, 0);
     if (loads) { fetch(kb0, q0); ch = hdr; if (nkb > 1) fetch(kb0 + 1, q1); }
     int issued = 0;
@@ -438,10 +442,13 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
       }
       uint8_t* brow = smem + (size_t)s * kStageBytes + MT * kATile + (size_t)p * 128;
       uint4 o[4];
+#ifdef MLXR_TUNING
       if (live && (P.debug & 1)) {
 #pragma unroll
         for (int i = 0; i < 4; i++) o[i] = cq;
-      } else if (live && QT != MLXR_Q4_K) {
+      } else
+#endif
+      if (live && QT != MLXR_Q4_K) {
         dequant32_other<QT, BF>(rowp, kb, hb, sh->nf4, P.vec_loads != 0, o);
       } else if (live) {
         // header: d, dmin (fp16), scales[12].  scales[3g .. 3g+2] of group g = (kb & 3) >> 1 as
@@ -661,7 +668,7 @@ int launch_prefill(const void* x, const void* w, const void* bias, void* y, int 
   P.S = S;
   P.vec_loads = ((((uintptr_t)w) & 15u) == 0 && ((size_t)N * P.row_bytes) % 16 == 0) ? 1 : 0;
   P.debug = 0;
-  if (const char* e = getenv("MLXR_TC_DEBUG")) P.debug = atoi(e);   // tuning probe
+  if (const char* e = tune_env("MLXR_TC_DEBUG")) P.debug = atoi(e);   // tuning probe
   const bool two = M > prefill::kBM;      // a second accumulator only pays when there are rows for it
   // kind::f16 needs A and B in one format: a bf16 x fp16 mix raised a CUDA error at launch, so
   // for bf16 activations the weights are rounded to bf16 as well

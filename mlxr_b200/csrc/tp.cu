@@ -14,6 +14,7 @@
 
 #include "../../include/mlxr_b200_tp.h"
 #include "common.cuh"
+#include "decode_kernel.cuh"   // bounded_wait
 #include "kernels.h"
 
 namespace mlxr {
@@ -74,7 +75,6 @@ constexpr size_t kFlagBytes = kTpFlagBytes;
 constexpr size_t kXchgBytes = kTpXchgBytes;
 static_assert(kTpSlotElems == MLXR_TP_PEER_MAX_ELEMS, "header and kernel disagree on the slot size");
 static_assert(kMaxCtas <= kTpFlagsPerRank, "flag index range");
-constexpr uint32_t kPeerSpinLimit = 1u << 24;   // bounded wait on a peer's flag
 
 struct PeerTable {
   char* base[kMaxWorld];
@@ -96,7 +96,8 @@ __device__ __forceinline__ uint32_t* flag_ptr(char* base, int src, int cta) {
 template <typename T>
 __global__ void __launch_bounds__(256) tp_exchange_kernel(const float* __restrict__ partial, T* __restrict__ y,
                                                           size_t n, size_t chunk, int rank, int world,
-                                                          PeerTable peers, uint32_t* ctl, int* status) {
+                                                          PeerTable peers, uint32_t* ctl, int* status,
+                                                          unsigned long long wait_ns) {
   const int b = blockIdx.x, tid = threadIdx.x;
   const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(ctl) + 1u;
   const int parity = (int)(seq & 1u);
@@ -118,12 +119,12 @@ __global__ void __launch_bounds__(256) tp_exchange_kernel(const float* __restric
   }
   if (tid < world) {
     const uint32_t* f = flag_ptr(peers.base[rank], tid, b);
-    bool ok = false;
-    for (uint32_t i = 0; i < kPeerSpinLimit; i++) {
+    // bounded by time (the limit every device-side wait of this library shares)
+    const bool ok = decode::bounded_wait([&] {
       uint32_t v;
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-      if ((int32_t)(v - seq) >= 0) { ok = true; break; }
-    }
+      return (int32_t)(v - seq) >= 0;
+    }, wait_ns);
     if (!ok) dead = 1;
   }
   __syncthreads();
@@ -167,8 +168,8 @@ struct mlxr_tp_ctx {
   size_t partial_elems = 0;
   char* xchg = nullptr;           // this rank's exchange buffer (null without the peer exchange)
   PeerTable peers;                // every rank's exchange buffer as mapped here
-  uint32_t* ctl = nullptr;        // [0] sequence number, [1] CTAs finished
-  char* handles_dev = nullptr;    // scratch for the handle all-gather
+  uint32_t* ctl = nullptr;        // [0] sequence number, [1] CTAs finished, [2] barrier / agreement word
+  char* handles_dev = nullptr;    // scratch for the handle all-gather (inside the control block)
   bool ready = false;             // set-up finished on this rank (destroy meets the peers only then)
 };
 
@@ -217,14 +218,36 @@ int mlxr_tp_create(const void* id128, int rank, int world, int use_peer, mlxr_tp
   c->rank = rank;
   c->world = world;
   for (int i = 0; i < kMaxWorld; i++) c->peers.base[i] = nullptr;
-  auto fail = [&](int rc) { mlxr_tp_destroy(c); return rc; };
-#define TRY_OR_FAIL(call) do { if (int rc_ = (call)) return fail(rc_); } while (0)
   auto cuda_step = [&](cudaError_t e, const char* what) -> int {
     if (e == cudaSuccess) return MLXR_OK;
     set_error("CUDA error %d (%s) at %s", (int)e, cudaGetErrorString(e), what);
     return MLXR_ERR_CUDA;
   };
-  TRY_OR_FAIL(cuda_step(cudaGetDevice(&c->device), "cudaGetDevice"));
+  // Set-up is collective and so is its outcome: a rank whose local step fails (an allocation, an
+  // IPC mapping) still takes part in every collective below, and the ranks agree on the result
+  // (minimum over ranks of a success flag) before anyone returns.  Otherwise the peers of a rank
+  // that left early would sit in a collective it never joins.  Only two failures cannot be
+  // shared: the 4 KB control block (allocated before the communicator exists) and
+  // ncclCommInitRank itself, which NCCL fails on all ranks together.
+  if (int rc = cuda_step(cudaGetDevice(&c->device), "cudaGetDevice")) { delete c; return rc; }
+  // control block: [0] sequence number, [1] CTAs finished, [2] float used by barriers and the
+  // agreement step; from byte 1024: the IPC handles of all ranks
+  if (int rc = cuda_step(cudaMalloc(&c->ctl, 4096), "cudaMalloc(ctl)")) { delete c; return rc; }
+  if (int rc = cuda_step(cudaMemset(c->ctl, 0, 4096), "cudaMemset(ctl)")) { cudaFree(c->ctl); delete c; return rc; }
+  c->handles_dev = reinterpret_cast<char*>(c->ctl) + 1024;
+  int local_rc = MLXR_OK;        // first local failure (its text stays in mlxr_last_error)
+  auto step = [&](int rc) { if (rc && !local_rc) local_rc = rc; return rc == MLXR_OK; };
+  step(ensure_partial(c, kSlotElems));
+  const bool want_peer = use_peer && world > 1;
+  cudaIpcMemHandle_t mine;
+  memset(&mine, 0, sizeof(mine));
+  if (want_peer) {
+    if (step(cuda_step(cudaMalloc(&c->xchg, kXchgBytes), "cudaMalloc(exchange buffer)")) &&
+        step(cuda_step(cudaMemset(c->xchg, 0, kFlagBytes), "cudaMemset(flags)")))
+      step(cuda_step(cudaIpcGetMemHandle(&mine, c->xchg), "cudaIpcGetMemHandle"));
+    step(cuda_step(cudaMemcpy(c->handles_dev + (size_t)rank * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice), "cudaMemcpy(handle)"));
+  }
+  step(cuda_step(cudaDeviceSynchronize(), "cudaDeviceSynchronize"));
   ncclUniqueId id;
   memcpy(&id, id128, sizeof(id));
   {
@@ -232,41 +255,50 @@ int mlxr_tp_create(const void* id128, int rank, int world, int use_peer, mlxr_tp
     if (r != ncclSuccess) {
       set_error("NCCL error %d (%s) at ncclCommInitRank", (int)r, g_nccl.GetErrorString(r));
       c->comm = nullptr;
-      return fail(MLXR_ERR_NCCL);
+      mlxr_tp_destroy(c);
+      return MLXR_ERR_NCCL;
     }
   }
-  TRY_OR_FAIL(cuda_step(cudaMalloc(&c->ctl, 64), "cudaMalloc(ctl)"));
-  TRY_OR_FAIL(cuda_step(cudaMemset(c->ctl, 0, 64), "cudaMemset(ctl)"));
-  TRY_OR_FAIL(ensure_partial(c, kSlotElems));
-  if (use_peer && world > 1) {
-    TRY_OR_FAIL(cuda_step(cudaMalloc(&c->xchg, kXchgBytes), "cudaMalloc(exchange buffer)"));
-    TRY_OR_FAIL(cuda_step(cudaMemset(c->xchg, 0, kFlagBytes), "cudaMemset(flags)"));
-    TRY_OR_FAIL(cuda_step(cudaMalloc(&c->handles_dev, (size_t)world * sizeof(cudaIpcMemHandle_t)), "cudaMalloc(handles)"));
-    cudaIpcMemHandle_t mine;
-    TRY_OR_FAIL(cuda_step(cudaIpcGetMemHandle(&mine, c->xchg), "cudaIpcGetMemHandle"));
-    TRY_OR_FAIL(cuda_step(cudaMemcpy(c->handles_dev + (size_t)rank * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice), "cudaMemcpy(handle)"));
-    TRY_OR_FAIL(cuda_step(cudaDeviceSynchronize(), "cudaDeviceSynchronize"));
-    {
-      ncclResult_t r = g_nccl.AllGather(c->handles_dev + (size_t)rank * sizeof(mine), c->handles_dev, sizeof(mine),
-                                        ncclInt8, c->comm, (cudaStream_t)0);
-      if (r != ncclSuccess) {
-        set_error("NCCL error %d (%s) at ncclAllGather(handles)", (int)r, g_nccl.GetErrorString(r));
-        return fail(MLXR_ERR_NCCL);
+  auto nccl_step = [&](ncclResult_t r, const char* what) -> int {
+    if (r == ncclSuccess) return MLXR_OK;
+    set_error("NCCL error %d (%s) at %s", (int)r, g_nccl.GetErrorString(r), what);
+    return MLXR_ERR_NCCL;
+  };
+  if (want_peer) {
+    // every rank joins the gather, whatever happened to it locally
+    step(nccl_step(g_nccl.AllGather(c->handles_dev + (size_t)rank * sizeof(mine), c->handles_dev, sizeof(mine), ncclInt8,
+                                    c->comm, (cudaStream_t)0), "ncclAllGather(handles)"));
+    step(cuda_step(cudaDeviceSynchronize(), "cudaDeviceSynchronize"));
+    cudaIpcMemHandle_t all[kMaxWorld];
+    if (!local_rc && step(cuda_step(cudaMemcpy(all, c->handles_dev, (size_t)world * sizeof(mine), cudaMemcpyDeviceToHost), "cudaMemcpy(handles)"))) {
+      for (int p = 0; p < world && !local_rc; p++) {
+        if (p == rank) { c->peers.base[p] = c->xchg; continue; }
+        void* ptr = nullptr;
+        if (step(cuda_step(cudaIpcOpenMemHandle(&ptr, all[p], cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle")))
+          c->peers.base[p] = (char*)ptr;
       }
     }
-    TRY_OR_FAIL(cuda_step(cudaDeviceSynchronize(), "cudaDeviceSynchronize"));
-    cudaIpcMemHandle_t all[kMaxWorld];
-    TRY_OR_FAIL(cuda_step(cudaMemcpy(all, c->handles_dev, (size_t)world * sizeof(mine), cudaMemcpyDeviceToHost), "cudaMemcpy(handles)"));
-    for (int p = 0; p < world; p++) {
-      if (p == rank) { c->peers.base[p] = c->xchg; continue; }
-      void* ptr = nullptr;
-      TRY_OR_FAIL(cuda_step(cudaIpcOpenMemHandle(&ptr, all[p], cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle"));
-      c->peers.base[p] = (char*)ptr;
+  }
+  // agreement: minimum over ranks of "my set-up succeeded"
+  {
+    const float ok_local = local_rc ? 0.0f : 1.0f;
+    float ok_all = 0.0f;
+    int rc = cuda_step(cudaMemcpy(c->ctl + 2, &ok_local, sizeof(float), cudaMemcpyHostToDevice), "cudaMemcpy(flag)");
+    if (!rc) rc = nccl_step(g_nccl.AllReduce(c->ctl + 2, c->ctl + 2, 1, ncclFloat32, ncclMin, c->comm, (cudaStream_t)0), "ncclAllReduce(agreement)");
+    if (!rc) rc = cuda_step(cudaMemcpy(&ok_all, c->ctl + 2, sizeof(float), cudaMemcpyDeviceToHost), "cudaMemcpy(flag)");
+    const float zero = 0.0f;
+    cudaMemcpy(c->ctl + 2, &zero, sizeof(float), cudaMemcpyHostToDevice);
+    if (rc || ok_all < 0.5f) {
+      // all ranks arrive here together: nobody is left inside a collective
+      if (!local_rc && !rc) set_error("mlxr_tp_create: set-up failed on another rank");
+      const int ret = local_rc ? local_rc : (rc ? rc : MLXR_ERR_CUDA);
+      c->ready = false;
+      mlxr_tp_destroy(c);
+      return ret;
     }
   }
   // nobody stores into a peer's buffer before every rank has cleared its flags and mapped all
-  TRY_OR_FAIL(ctx_barrier(c, (cudaStream_t)0));
-#undef TRY_OR_FAIL
+  if (int rc = ctx_barrier(c, (cudaStream_t)0)) { mlxr_tp_destroy(c); return rc; }
   c->ready = true;
   *out = c;
   return MLXR_OK;
@@ -281,7 +313,6 @@ int mlxr_tp_destroy(mlxr_tp_ctx* c) {
     if (p != c->rank && c->peers.base[p]) cudaIpcCloseMemHandle(c->peers.base[p]);
   if (c->ready) ctx_barrier(c, (cudaStream_t)0);
   if (c->xchg) cudaFree(c->xchg);
-  if (c->handles_dev) cudaFree(c->handles_dev);
   if (c->partial) cudaFree(c->partial);
   if (c->ctl) cudaFree(c->ctl);
   if (c->comm) g_nccl.CommDestroy(c->comm);
@@ -344,7 +375,8 @@ int mlxr_tp_all_reduce(mlxr_tp_ctx* c, const float* partial, void* y, size_t n, 
     size_t chunk = (n + grid - 1) / grid;
     chunk = (chunk + 3) / 4 * 4;
     MLXR_DISPATCH_DTYPE(dtype, T, {
-      tp_exchange_kernel<T><<<grid, 256, 0, st>>>(partial, (T*)y, n, chunk, c->rank, c->world, c->peers, c->ctl, status);
+      tp_exchange_kernel<T><<<grid, 256, 0, st>>>(partial, (T*)y, n, chunk, c->rank, c->world, c->peers, c->ctl, status,
+                                                  wait_limit_ns());
     });
     MLXR_LAUNCH_CHECK("tp_exchange_kernel");
     return MLXR_OK;
@@ -368,6 +400,39 @@ int mlxr_tp_all_reduce(mlxr_tp_ctx* c, const float* partial, void* y, size_t n, 
   return MLXR_ERR_INVALID_ARGUMENT;
 }
 
+size_t mlxr_tp_exchange_buffer_bytes(void) { return kXchgBytes; }
+
+int mlxr_tp_all_reduce_buffers(const float* partial, void* y, size_t n, int dtype, int rank, int world,
+                               void* const* buffers, uint32_t* ctl, void* stream) {
+  if (!partial || !y || !buffers || !ctl) { set_error("null pointer"); return MLXR_ERR_INVALID_ARGUMENT; }
+  if (dtype != MLXR_F16 && dtype != MLXR_BF16 && dtype != MLXR_F32) { set_error("bad dtype %d", dtype); return MLXR_ERR_INVALID_ARGUMENT; }
+  if (world < 2 || world > kMaxWorld || rank < 0 || rank >= world) {
+    set_error("rank %d / world %d outside 2..%d", rank, world, kMaxWorld);
+    return MLXR_ERR_INVALID_ARGUMENT;
+  }
+  if (n == 0) return MLXR_OK;
+  if (n > kSlotElems || n % 4 != 0) {
+    set_error("peer exchange needs n %% 4 == 0 and n <= %zu (got %zu)", kSlotElems, n);
+    return MLXR_ERR_SHAPE;
+  }
+  PeerTable peers;
+  for (int i = 0; i < kMaxWorld; i++) peers.base[i] = i < world ? (char*)buffers[i] : nullptr;
+  for (int i = 0; i < world; i++)
+    if (!peers.base[i] || ((uintptr_t)peers.base[i] & 15u)) { set_error("exchange buffer %d is null or not 16-byte aligned", i); return MLXR_ERR_INVALID_ARGUMENT; }
+  cudaStream_t st = (cudaStream_t)stream;
+  int* status = nullptr;
+  if (int r = stream_status_word(st, &status)) return r;
+  int grid = (int)((n + 1023) / 1024);
+  if (grid > kMaxCtas) grid = kMaxCtas;
+  size_t chunk = (n + grid - 1) / grid;
+  chunk = (chunk + 3) / 4 * 4;
+  MLXR_DISPATCH_DTYPE(dtype, T, {
+    tp_exchange_kernel<T><<<grid, 256, 0, st>>>(partial, (T*)y, n, chunk, rank, world, peers, ctl, status, wait_limit_ns());
+  });
+  MLXR_LAUNCH_CHECK("tp_exchange_kernel");
+  return MLXR_OK;
+}
+
 int mlxr_tp_mlp_block(mlxr_tp_ctx* c, const void* x, const void* norm_weight, const void* wg, const void* wu,
                       const void* wd, void* y, int M, int hidden, int inter, int qt, float eps, int dtype,
                       int exchange, void* stream) {
@@ -380,7 +445,7 @@ int mlxr_tp_mlp_block(mlxr_tp_ctx* c, const void* x, const void* norm_weight, co
   if (M == 0) return MLXR_OK;
   const size_t n = (size_t)M * hidden;
   if (c->world > 1 && c->xchg && (exchange == MLXR_TP_EXCHANGE_AUTO || exchange == MLXR_TP_EXCHANGE_PEER) &&
-      n <= kSlotElems && !getenv("MLXR_TP_NO_FUSE")) {
+      n <= kSlotElems && !tune_env("MLXR_TP_NO_FUSE")) {
     // decode shapes: one launch computes the rank's share, stores its sums into every rank's
     // exchange buffer from the epilogue and ends with the reduction
     DecodeTp tp;

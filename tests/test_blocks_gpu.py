@@ -56,7 +56,7 @@ def test_mlp_without_norm(oracle):
     assert e_ref <= TOL and e_truth <= TOL
 
 
-@pytest.mark.parametrize("M", [1, 8, 32])
+@pytest.mark.parametrize("M", [1, 8, 32, 64])
 def test_llama3_8b_qkv_rope(oracle, M):
     """q 4096x4096, k/v 1024x4096, Q4_K, bf16, theta 5e5, positions uniform in [0, 8192)."""
     import mlxr_b200 as mx
