@@ -17,6 +17,11 @@ roofline  algorithmic bytes of one step / measured step time vs the measured HBM
 cpu_baseline  the oracle's restatement of the reference CPU path (full dequant + scalar
           triple loop, one thread) timed on this box's host cores
 
+parity    the first step is checked against the oracle composition (and, on several GPUs, for
+          identical results on all ranks) before anything is timed; failure ends the run
+secondary the other parts of the benchmark definition (prefill Q-GEMM TFLOP/s, GEMV GB/s per
+          format, the TinyLlama- and the 70B-shaped block), each with its own roofline
+
 Weights rotate through several device copies so that consecutive steps cannot be served
 from the 126 MB L2 (the block's weights are 99 MB).
 """
@@ -106,27 +111,34 @@ class ClockSampler:
             self.thread = threading.Thread(target=self._run, daemon=True)
             self.thread.start()
 
+    def window(self, t0, t1):
+        """Summary of the samples taken between two perf_counter readings (sampling continues)."""
+        return self._summary([s for s in list(self.samples) if t0 <= s[0] <= t1])
+
     def stop(self, t0=None, t1=None):
         self.stop_flag = True
         if self.thread:
             self.thread.join(timeout=1.0)
-        if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
         sel = [s for s in self.samples if t0 is not None and t0 <= s[0] <= t1] or self.samples
+        return self._summary(sel)
+
+    def _summary(self, sel):
+        if not sel:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
         names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
                  0x80: "hw_power_brake"}
         bits = 0
-        for s in sel:
-            bits |= s[2]
-        return {"sm_mhz": float(np.median([s[1] for s in sel])), "sm_max_mhz": self.max_mhz,
+        for smp in sel:
+            bits |= smp[2]
+        return {"sm_mhz": float(np.median([smp[1] for smp in sel])), "sm_max_mhz": self.max_mhz,
                 "reasons": [n for b, n in names.items() if bits & b], "samples": len(sel)}
 
 
 def cpu_baseline(M: int, budget_s: float = 20.0):
-    H, I = SIZES["hidden"], SIZES["inter"]
     """Oracle port of the reference CPU path (QGemmDequantPrimitive::eval_cpu: full dequant to
     fp32, then the scalar m/n/k loop, single thread) for the whole MLP block at batch M,
-    repeated while the time budget lasts."""
+    repeated while the time budget lasts.  Returns (record, seconds per step, repetitions)."""
+    H, I = SIZES["hidden"], SIZES["inter"]
     from oracle import oracle as O
     wg, wu, wd, x, gamma = make_inputs(M, H, I)
     xb = O.round_to(x, O.BF16)
@@ -149,39 +161,224 @@ def cpu_baseline(M: int, budget_s: float = 20.0):
     return {"value": M / t, "unit": "tokens/s", "cores": 1, "kind": "port",
             "sample": f"full MLP block at batch {M}, {len(times)} repetitions, median {t * 1e3:.1f} ms/step "
                       f"(oracle restatement of eval_cpu: full dequant + scalar loop; the reference's own "
-                      f"eval_cpu throws for Q4_K)"}, t
+                      f"eval_cpu throws for Q4_K)"}, t, len(times)
+
+
+def cpu_baseline_all_cores(M: int, budget_s: float = 10.0):
+    """The same block as a fair CPU composition on all host cores: the oracle's dequantizers, then
+    fp32 BLAS matrix products and fp32 elementwise steps (oracle.mlp_block).  A stated baseline."""
+    H, I = SIZES["hidden"], SIZES["inter"]
+    from oracle import oracle as O
+    wg, wu, wd, x, gamma = make_inputs(M, H, I)
+    xb = O.round_to(x, O.BF16)
+    gb = O.round_to(gamma, O.BF16)
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while (time.perf_counter() < t_end and len(times) < 10) or not times:
+        t0 = time.perf_counter()
+        O.mlp_block(xb, gb, wg, wu, wd, I, QT_Q4_K, EPS, O.BF16)
+        times.append(time.perf_counter() - t0)
+    t = float(np.median(times))
+    return {"value": M / t, "unit": "tokens/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"full MLP block at batch {M}, {len(times)} repetitions, median {t * 1e3:.1f} ms/step "
+                      f"(oracle dequantizers + fp32 BLAS products on all host cores)"}
 
 
 def run_reference(args):
+    """The reference arm: the reference's CPU path for the same block (oracle port of eval_cpu, one
+    thread: that path is single-threaded by construction), a bounded number of repetitions.  The
+    line reports the repetitions actually run as `steps`."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     M = args.batch
-    steps = max(1, min(args.steps, 20))
-    cb, t = cpu_baseline(M, budget_s=min(60.0, 3.0 * steps))
+    want = max(1, min(args.steps, 5))
+    cb, t, reps = cpu_baseline(M, budget_s=min(60.0, 12.0 * want))
     line = {
         "impl": "reference", "metric": "mlp_decode_tokens_per_s", "value": cb["value"], "unit": "tokens/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
+        "n_gpus": args.gpus, "steps": reps, "steps_requested": args.steps, "warmup": 0, "ms_per_step": t * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": config_dict(M, 1, 0),
+        "config": config_dict(M, max(1, args.gpus), args.exchange if args.gpus > 1 else None),
         "cpu_baseline": cb,
+        "cpu_baseline_all_cores": None if args.no_cpu else cpu_baseline_all_cores(M, budget_s=8.0),
         "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
 
 
-def config_dict(M, n_gpus, copies, exchange=None):
+def config_dict(M, n_gpus, exchange=None):
+    """The workload's name: the same dict for both arms (nothing that depends on the run)."""
     H, I = SIZES["hidden"], SIZES["inter"]
     name = {(4096, 14336): "Llama-3-8B", (8192, 28672): "Llama-3-70B", (2048, 5632): "TinyLlama"}.get((H, I), "custom")
-    mb = copies * (3 * H * I * 144 // 256) // n_gpus // 1000000
     d = {"workload": f"{name}-shaped Q4_K decode MLP block (hidden {H}, intermediate {I}, RMSNorm prologue, "
                      f"SwiGLU), batch {M}, bf16 activations",
          "batch": M, "quant": "Q4_K (MLXR layout)",
          "parallelism": "single GPU" if n_gpus == 1 else f"tp{n_gpus} (gate/up rows and down columns sharded, one sum over ranks per step)",
-         "l2": f"weights rotate over {copies} device copies per GPU ({mb} MB per GPU; L2 is 126 MB)"}
+         "l2": "weights rotate over several device copies per GPU (more than 700 MB per GPU; L2 is 126 MB)"}
     if exchange:
         d["exchange"] = exchange
     return d
+
+
+def timed_graph(step, K, W, stream, min_seconds=0.25, max_repeats=400, dist=None):
+    """Capture K calls of step(i, stream_handle) into one CUDA graph on `stream` and replay it until
+    at least `min_seconds` of device time have been timed (every replay between its own pair of
+    CUDA events on the launching stream).  Returns (median ms per step, repeats, launches counted
+    during capture, timed seconds, (t0, t1) wall-clock bracket for the clock sampler)."""
+    import torch
+    from mlxr_b200._capi import lib
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        for i in range(W):
+            step(i, stream.cuda_stream)
+        stream.synchronize()
+        l0 = lib.mlxr_launch_count()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(K):
+                step(W + i, torch.cuda.current_stream().cuda_stream)
+        launches = lib.mlxr_launch_count() - l0
+        graph.replay()          # untimed: the first replay uploads the graph
+        stream.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        times = []
+        total = 0.0
+        t0 = time.perf_counter()
+        while total < min_seconds * 1e3 and len(times) < max_repeats:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+            ms = e0.elapsed_time(e1)
+            times.append(ms)
+            total += ms
+            if dist is not None:
+                # all ranks leave the loop together (rank 0 decides)
+                flag = torch.tensor([1.0 if total < min_seconds * 1e3 and len(times) < max_repeats else 0.0], device="cuda")
+                dist.broadcast(flag, 0)
+                if flag.item() == 0.0:
+                    break
+        t1 = time.perf_counter()
+    torch.cuda.synchronize()
+    return float(np.median(times)) / K, len(times), int(launches), total * 1e-3, (t0, t1)
+
+
+def random_packed(N, K, qt, device, seed):
+    """Packed weights for TIMING ONLY: random block bytes with every fp16 field set to a small
+    finite constant (quantizing N(0, 0.02) matrices of the larger secondary workloads on the host
+    would take minutes; the kernels' time does not depend on the values)."""
+    import torch
+    be, bb = {0: (32, 18), 2: (32, 34), 3: (256, 144), 16: (64, 34)}[qt]
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    w = torch.randint(0, 256, (N * (K // be), bb), dtype=torch.uint8, device=device, generator=g)
+    w[:, 0] = 0x1F
+    w[:, 1] = 0x20           # fp16 0x201F = 0.0080
+    if qt == 3:
+        w[:, 2] = 0x1F
+        w[:, 3] = 0x1C       # dmin = 0.0040
+    return w.reshape(-1)
+
+
+def secondary_measurements(world, rank, local, ctx, args, dist):
+    """The other parts of the benchmark definition, each as its own small measurement with its own
+    roofline: prefill Q-GEMM (TFLOP/s against the measured bf16 peak), the M = 1 GEMV per format
+    (GB/s against the measured HBM peak), the TinyLlama-shaped block, and the Llama-3-70B-shaped
+    block at batch 1 and 32 on this number of GPUs.  Single-GPU entries run on rank 0 only."""
+    import torch
+    from mlxr_b200._capi import check, lib
+    hbm, tf, which = measured_peaks()
+    dev = torch.device("cuda", local)
+    out = []
+    side = torch.cuda.Stream()
+    sampler = ClockSampler(local)
+    sampler.start()
+
+    def clocks_of(bracket):
+        c = sampler.window(*bracket)
+        return c
+
+    def linear_entry(fmt, M, N, K, min_s):
+        qt = FORMATS[fmt]
+        wbytes = int(lib.mlxr_quantized_weight_size(N, K, qt))
+        copies = max(2, int(np.ceil(300e6 / wbytes))) if M <= 64 else 1
+        ws = [random_packed(N, K, qt, dev, 100 + i) for i in range(copies)]
+        xcopies = 1 if M <= 64 else max(2, int(np.ceil(300e6 / (M * K * 2))))
+        xs = [torch.randn((M, K), device=dev, dtype=torch.float32).bfloat16() for _ in range(min(xcopies, 8))]
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        gs = lib.mlxr_default_group_size(qt)
+
+        def step(i, st):
+            check(lib.mlxr_q_gemm_dequant(xs[i % len(xs)].data_ptr(), ws[i % len(ws)].data_ptr(), None, y.data_ptr(), M, N, K, qt, gs, 1, st))
+
+        K_steps = 50 if M <= 64 else 5
+        ms, reps, launches, secs, bracket = timed_graph(step, K_steps, 3, side, min_seconds=min_s)
+        ab = wbytes + 2 * M * (K + N)
+        flops = 2.0 * M * N * K
+        gbs, tfl = ab / (ms * 1e-3) / 1e9, flops / (ms * 1e-3) / 1e12
+        tensor = M >= 256
+        roof = ({"bound": "tensor", "achieved": tfl, "peak": tf, "unit": "TFLOP/s", "frac": tfl / tf, "traffic": None}
+                if tensor else
+                {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "traffic": None})
+        roof["peak_source"] = which
+        return {"name": f"{'prefill Q-GEMM' if tensor else 'decode GEMV'} {fmt} [{M}, {K}] x [{N}, {K}]^T",
+                "metric": "prefill_qgemm_tflops" if tensor else "qgemv_hbm_gbs", "value": tfl if tensor else gbs,
+                "unit": "TFLOP/s" if tensor else "GB/s", "us_per_step": ms * 1e3, "steps": K_steps, "repeats": reps,
+                "gpu_launches": launches, "roofline": roof, "clocks": clocks_of(bracket), "data": "random packed blocks (timing only)"}
+
+    def block_entry(name, hidden, inter, qt, M, dtype_code, tdt, min_s, tp):
+        n_gpus = world if tp else 1
+        wsz_gu = int(lib.mlxr_quantized_weight_size(inter // n_gpus, hidden, qt))
+        wsz_d = int(lib.mlxr_quantized_weight_size(hidden, inter // n_gpus, qt))
+        per_copy = 2 * wsz_gu + wsz_d
+        copies = max(1, int(np.ceil(300e6 / per_copy)))
+        sets = [(random_packed(inter // n_gpus, hidden, qt, dev, 200 + 3 * i), random_packed(inter // n_gpus, hidden, qt, dev, 201 + 3 * i),
+                 random_packed(hidden, inter // n_gpus, qt, dev, 202 + 3 * i)) for i in range(copies)]
+        x = torch.randn((M, hidden), device=dev, dtype=torch.float32).to(tdt)
+        if tp and n_gpus > 1:
+            dist.broadcast(x, 0)
+        gam = torch.ones(hidden, device=dev, dtype=tdt)
+        y = torch.empty_like(x)
+
+        def step(i, st):
+            a, b, c = sets[i % copies]
+            if tp and n_gpus > 1:
+                check(lib.mlxr_tp_mlp_block(ctx._h, x.data_ptr(), gam.data_ptr(), a.data_ptr(), b.data_ptr(), c.data_ptr(),
+                                            y.data_ptr(), M, hidden, inter, qt, EPS, dtype_code, 0, st))
+            else:
+                check(lib.mlxr_mlp_block(x.data_ptr(), gam.data_ptr(), a.data_ptr(), b.data_ptr(), c.data_ptr(),
+                                         y.data_ptr(), M, hidden, inter, qt, EPS, dtype_code, st))
+
+        K_steps = 20
+        ms, reps, launches, secs, bracket = timed_graph(step, K_steps, 3, side, min_seconds=min_s, dist=dist if (tp and n_gpus > 1) else None)
+        if tp and n_gpus > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        ab = per_copy + 2 * M * hidden * 2 + hidden * 2
+        gbs = ab / (ms * 1e-3) / 1e9
+        return {"name": name, "metric": "mlp_decode_tokens_per_s", "value": M / (ms * 1e-3), "unit": "tokens/s",
+                "n_gpus": n_gpus, "us_per_step": ms * 1e3, "steps": K_steps, "repeats": reps, "gpu_launches": launches,
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s", "frac": gbs / hbm, "traffic": None,
+                             "per": "GPU", "algorithmic_bytes_per_step": ab, "peak_source": which},
+                "clocks": clocks_of(bracket), "data": "random packed blocks (timing only)"}
+
+    if rank == 0:
+        out.append(linear_entry("q4_k", 2048, 14336, 4096, 0.05))
+        out.append(linear_entry("q4_k", 8192, 14336, 4096, 0.05))
+        for fmt in ("q4_k", "q4_0", "q8_0", "nf4"):
+            out.append(linear_entry(fmt, 1, 14336, 4096, 0.03))
+        out.append(block_entry("TinyLlama-shaped Q4_0 decode MLP block, batch 1, fp16", 2048, 5632, 0, 1, 0, torch.float16, 0.03, False))
+    # the 70B-shaped block on this number of GPUs (every rank takes part)
+    for M in (1, 32):
+        e = block_entry(f"Llama-3-70B-shaped Q4_K decode MLP block, batch {M}, bf16, {world} GPU(s)", 8192, 28672, QT_Q4_K, M, 1,
+                        torch.bfloat16, 0.05, True)
+        if rank == 0:
+            out.append(e)
+    sampler.stop()
+    return out
 
 
 def run_mine(args):
@@ -204,7 +401,8 @@ def run_mine(args):
     shard_mb = 3 * H * I * 144 // 256 // world / 1e6
     copies = int(min(64, max(8, np.ceil(800.0 / shard_mb))))
 
-    wg, wu, wd, x, gamma = make_inputs(M, H, I)
+    wg_full, wu_full, wd_full, x, gamma = make_inputs(M, H, I)
+    wg, wu, wd = wg_full, wu_full, wd_full
     dev = torch.device("cuda", local)
     ctx = None
     exchange = {"auto": 0, "nccl_f32": 1, "nccl_act": 2, "peer": 3}[args.exchange]
@@ -218,10 +416,9 @@ def run_mine(args):
     xt = torch.from_numpy(x).bfloat16().to(dev)
     gt = torch.from_numpy(gamma).bfloat16().to(dev)
     y = torch.empty_like(xt)
-    st = torch.cuda.current_stream().cuda_stream
     status = ctypes.c_int(0)
 
-    def step(i):
+    def step(i, st):
         a, b, c = wsets[i % copies]
         if ctx is None:
             check(lib.mlxr_mlp_block(xt.data_ptr(), gt.data_ptr(), a.data_ptr(), b.data_ptr(), c.data_ptr(),
@@ -230,56 +427,74 @@ def run_mine(args):
             check(lib.mlxr_tp_mlp_block(ctx._h, xt.data_ptr(), gt.data_ptr(), a.data_ptr(), b.data_ptr(), c.data_ptr(),
                                         y.data_ptr(), M, H, I, QT_Q4_K, EPS, 1, exchange, st))
 
+    # ---- parity gate, before anything is timed: the result of one step against the oracle's
+    # composition on rank 0, and - for the exchanges that add the ranks' sums in rank order -
+    # bit-identical results on all ranks.  A failure ends the run with a non-zero exit code.
+    st0 = torch.cuda.current_stream().cuda_stream
+    step(0, st0)
+    torch.cuda.synchronize()
+    parity = {"tol": 2e-2}
+    if world > 1:
+        ys = [torch.empty_like(y) for _ in range(world)]
+        dist.all_gather(ys, y)
+        identical = all(torch.equal(ys[0], t) for t in ys)
+        parity["ranks_identical"] = bool(identical)
+        parity["ranks_identical_required"] = exchange in (0, 3)
+    if rank == 0:
+        from oracle import oracle as O
+        ref = O.mlp_block(O.round_to(x, O.BF16), O.round_to(gamma, O.BF16), wg_full, wu_full, wd_full, I, QT_Q4_K, EPS, O.BF16)
+        parity["rel_l2"] = O.rel_l2(y.float().cpu().numpy(), ref)
+        parity["against"] = "oracle composition of the unsharded block (fp32, bf16 rounding at each materialised array)"
+    ok = torch.tensor([1.0], device=dev)
+    if rank == 0 and not (parity["rel_l2"] <= parity["tol"]):
+        ok[0] = 0.0
+    if world > 1 and parity["ranks_identical_required"] and not parity["ranks_identical"]:
+        ok[0] = 0.0
+    if world > 1:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if ok.item() == 0.0:
+        if rank == 0:
+            print(json.dumps({"error": "parity gate failed", "parity": parity}))
+        sys.exit(3)
+
     # The K timed steps are captured once into a CUDA graph and replayed: at ~20-30 us per
-    # step a Python/ctypes launch loop would measure the host, not the GPU.  The NCCL exchange
-    # modes are timed with plain launches instead (a library collective per step dominates there).
+    # step a Python/ctypes launch loop would measure the host, not the GPU.  The graph is replayed
+    # until a quarter of a second of device time has been timed; the value is the median replay.
+    # The NCCL exchange modes are timed with plain launches instead (a library collective per step
+    # dominates there).
     use_graph = ctx is None or exchange in (0, 3)
     side = torch.cuda.Stream()
-    graph = torch.cuda.CUDAGraph() if use_graph else None
-    with torch.cuda.stream(side):
-        st = side.cuda_stream
-        for i in range(W):
-            step(i)
-        side.synchronize()
-        l_cap0 = lib.mlxr_launch_count()
-        if use_graph:
-            with torch.cuda.graph(graph, stream=side):
-                st = torch.cuda.current_stream().cuda_stream
-                for i in range(K):
-                    step(W + i)
-            launches = lib.mlxr_launch_count() - l_cap0
-        st = side.cuda_stream
     sampler = ClockSampler(local)
     sampler.start()
-    with torch.cuda.stream(side):
-        if use_graph:
-            graph.replay()          # untimed: first replay uploads the graph
-        side.synchronize()
-        if world > 1:
+    if use_graph:
+        ms_step, repeats, launches, timed_s, bracket = timed_graph(step, K, W, side, min_seconds=0.25,
+                                                                   dist=dist if world > 1 else None)
+    else:
+        with torch.cuda.stream(side):
+            for i in range(W):
+                step(i, side.cuda_stream)
+            side.synchronize()
             dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0 = time.perf_counter()
-        e0.record(side)
-        if use_graph:
-            graph.replay()
-        else:
+            torch.cuda.synchronize()
+            l0 = lib.mlxr_launch_count()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            e0.record(side)
             for i in range(K):
-                step(W + i)
-            launches = lib.mlxr_launch_count() - l_cap0
-        e1.record(side)
-        side.synchronize()
-        t1 = time.perf_counter()
+                step(W + i, side.cuda_stream)
+            e1.record(side)
+            side.synchronize()
+            t1 = time.perf_counter()
+            launches = lib.mlxr_launch_count() - l0
+        ms_step, repeats, timed_s, bracket = e0.elapsed_time(e1) / K, 1, e0.elapsed_time(e1) * 1e-3, (t0, t1)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    ms = e0.elapsed_time(e1)
-    clocks = sampler.stop(t0, t1)
+    clocks = sampler.stop(*bracket)
     if world > 1:
-        t = torch.tensor([ms], device=dev)
+        t = torch.tensor([ms_step], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    ms_step = ms / K
+        ms_step = float(t.item())
     st = torch.cuda.current_stream().cuda_stream
 
     # end to end: host buffers, copies inside the timed region, every step
@@ -304,7 +519,7 @@ def run_mine(args):
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    Ke = min(K, 2000)
+    Ke = max(K, 200)
     th0 = time.perf_counter()
     for i in range(Ke):
         step_host(i)
@@ -320,30 +535,41 @@ def run_mine(args):
     check(lib.mlxr_stream_status(side.cuda_stream, ctypes.byref(status)))
     assert status.value == 0, f"device status {status.value} after the timed region"
 
+    secondary = None
+    if not args.no_secondary:
+        secondary = secondary_measurements(world, rank, local, ctx, args, dist if world > 1 else None)
+
     if rank == 0:
         hbm, _, which = measured_peaks()
         # per GPU: its share of the weights plus the replicated activations
         ab = (algorithmic_bytes(M, H, I) - 2 * M * H * 2 - H * 2) // world + 2 * M * H * 2 + H * 2
         achieved = ab / (ms_step * 1e-3) / 1e9
-        cb = None
+        cb = cb_all = None
         if world == 1 and not args.no_cpu:
-            cb, _ = cpu_baseline(M, budget_s=args.cpu_seconds)
+            cb, _, _ = cpu_baseline(M, budget_s=args.cpu_seconds)
+            cb_all = cpu_baseline_all_cores(M, budget_s=8.0)
         line = {
             "metric": "mlp_decode_tokens_per_s", "value": M / (ms_step * 1e-3),
             "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_step,
+            "repeats": repeats, "timed_seconds": timed_s,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": config_dict(M, world, copies, args.exchange if world > 1 else None),
+            "config": config_dict(M, world, args.exchange if world > 1 else None),
+            "weight_copies_per_gpu": copies,
+            "parity": parity,
             "e2e": {"value": M / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": M * H * 2, "d2h_bytes_per_step": M * H * 2,
-                    "ms_per_step": e2e_s * 1e3},
-            "gpu_launches": int(launches),
+                    "ms_per_step": e2e_s * 1e3, "steps": Ke},
+            "gpu_launches": int(launches) * int(repeats),
+            "gpu_launches_per_replay": int(launches),
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
                          "traffic": TRAFFIC.get((H, I, M)) if world == 1 else None, "peak_source": which,
                          "algorithmic_bytes_per_step": ab, "per": "GPU",
                          "kernel": "decode_kernel (one persistent launch per step: RMSNorm + gate/up + SwiGLU + down)"
-                                   + ("" if world == 1 else " + tp_exchange_kernel"),
-                         "timing": "CUDA events around " + ("a CUDA-graph replay of the K steps" if use_graph else "K plain launches")},
+                                   + ("" if world == 1 else " + exchange of the ranks' sums"),
+                         "timing": "CUDA events around " + (f"each of {repeats} CUDA-graph replays of the K steps (median)" if use_graph else "K plain launches")},
             "cpu_baseline": cb,
+            "cpu_baseline_all_cores": cb_all,
+            "secondary": secondary,
         }
         print(json.dumps(line))
     if ctx is not None:
@@ -517,11 +743,12 @@ def run_sweep(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="mine", choices=["mine", "reference"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary measurements (prefill, GEMV per format, other blocks)")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--hidden", type=int, default=H)
     ap.add_argument("--inter", type=int, default=I)

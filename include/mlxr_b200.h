@@ -67,7 +67,20 @@ typedef enum mlxr_quant_type {
   MLXR_Q5_0 = 5, MLXR_Q5_1 = 6, MLXR_Q8_1 = 7, MLXR_Q2_K = 8, MLXR_Q3_K = 9,
   MLXR_Q5_K = 10, MLXR_Q8_K = 11, MLXR_IQ2_XXS = 12, MLXR_IQ2_XS = 13,
   MLXR_IQ3_XXS = 14, MLXR_IQ3_S = 15,
-  MLXR_NF4 = 16
+  MLXR_NF4 = 16,
+  /* Extension: the CANONICAL ggml layouts, as a .gguf file stores them (the reference parses such
+   * files, daemon/registry/gguf_parser.h:141-211, but its loader skips quantized tensors because
+   * its kernels cannot read them, daemon/server/model_loader.cpp:236-245):
+   *   GGML_Q4_0  18 B / 32:  fp16 d, qs[16]; element i = low nibble of qs[i], i+16 = high nibble;
+   *                          w = (q - 8) * d
+   *   GGML_Q4_K 144 B / 256: fp16 d, fp16 dmin, scales[12] = eight 6-bit (scale, min) pairs
+   *                          (get_scale_min_k4 packing), qs[128]; 64-element chunk j: elements
+   *                          0..31 = low nibbles of qs[32j..32j+31], 32..63 = high nibbles;
+   *                          w = (d * sc) * q - dmin * m in float32
+   * Dequantized values equal gguf.quants.dequantize bit for bit.  mlxr_dequantize and
+   * mlxr_q_gemm_dequant accept them (any batch); canonical Q4_0 can also be turned into MLXR's
+   * Q4_0 on the device without loss (mlxr_repack_ggml_q4_0) to run on the fast kernels. */
+  MLXR_GGML_Q4_0 = 32, MLXR_GGML_Q4_K = 33
 } mlxr_quant_type;
 
 /* RoPEScalingMode, rope_apply_primitive.h:18-23 */
@@ -161,6 +174,31 @@ MLXR_API int mlxr_rope_apply(const void* x, const uint16_t* cos_f16, const uint1
                              int heads, int head_dim, int max_seq_len, int mode,
                              float scale_factor, int position_offset, int dtype,
                              int check, void* stream);
+
+/* RoPE in the split-half ("rotate_half") convention of graph::RotaryEmbedding
+ * (core/graph/layers.cpp:113-225), which differs from the rope_apply primitive above: the head
+ * is split into its first and second half (x1, x2), the tables are float32 [max_seq_len, dim/2]
+ * with freq_i = 1 / base^(2i/dim) and angle = pos * freq_i (compute_freqs, :121-154), positions
+ * are the contiguous range offset .. offset + seq, and
+ *   y1 = x1*cos - x2*sin,  y2 = x2*cos + x1*sin      (forward, :196-222)
+ * with every product and sum rounded to float32 like the composition of MLX ops, then one
+ * rounding to `dtype`.  x, y: [batch, seq, heads, head_dim]; y may alias x.  The host function
+ * fills the tables (HOST memory) exactly as compute_freqs does. */
+MLXR_API int mlxr_rope_tables_f32_host(float* cos_f32, float* sin_f32, int max_seq_len, int dim,
+                                       float base);
+MLXR_API int mlxr_rope_apply_split_half(const void* x, const float* cos_f32, const float* sin_f32,
+                                        void* y, int batch, int seq, int heads, int head_dim,
+                                        int max_seq_len, int offset, int dtype, void* stream);
+
+/* y[M, N] = x[M, K] W^T (+ bias) with a DENSE weight [N, K] of the activation dtype:
+ * graph::Linear::forward (core/graph/layers.cpp:86-99), the op the quantized linear replaces.
+ * fp32 accumulation, one rounding at the store.  Not the quantized hot path. */
+MLXR_API int mlxr_linear_dense(const void* x, const void* weight, const void* bias, void* y, int M,
+                               int N, int K, int dtype, void* stream);
+
+/* Canonical ggml Q4_0 blocks [N, K] -> MLXR Q4_0 blocks (a permutation of nibbles inside every
+ * block: value-preserving).  src and dst may not overlap.  Extension, see MLXR_GGML_Q4_0. */
+MLXR_API int mlxr_repack_ggml_q4_0(const void* ggml_blocks, void* mlxr_blocks, int N, int K, void* stream);
 
 /* ---- fused decoder-layer pieces ----------------------------------------------------
  * MLP block: y = down( SiLU(gate(n)) * up(n) ),  n = rmsnorm(x, norm_weight, eps) when

@@ -11,7 +11,7 @@ the shared library exists.
 from .types import QuantType, RoPEScalingMode  # noqa: F401
 
 _OPS = ("compute_quantized_weight_size", "compute_rope_tables", "dequantize", "mlp_block", "mlp_block_partial", "q_gemm_dequant",
-        "qkv_rope", "quant_type_name", "rmsnorm_fused", "rope_apply", "swiglu", "swish", "swiglu_mlp")
+        "qkv_rope", "quant_type_name", "rmsnorm_fused", "rope_apply", "swiglu", "swish", "swiglu_mlp", "RotaryEmbedding", "linear", "repack_ggml_q4_0")
 
 
 def __getattr__(name):

@@ -40,6 +40,10 @@ PROTOTYPES = {
     "mlxr_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "mlxr_swiglu": (_i, [_vp, _vp, _vp, _sz, _i, _vp]),
     "mlxr_rope_apply": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp]),
+    "mlxr_repack_ggml_q4_0": (_i, [_vp, _vp, _i, _i, _vp]),
+    "mlxr_rope_tables_f32_host": (_i, [_vp, _vp, _i, _i, _f]),
+    "mlxr_rope_apply_split_half": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "mlxr_linear_dense": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "mlxr_mlp_block": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp]),
     "mlxr_mlp_block_partial_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _vp]),
     "mlxr_mlp_block_dense": (_i, [_vp] * 8 + [_i, _i, _i, _i, _vp]),

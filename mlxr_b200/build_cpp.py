@@ -1,5 +1,6 @@
-"""Build the C++ primitive layer: lib/libmlxr_primitives.so (MLXR's Primitive classes and free
-functions over the C ABI, compiled against the MLX stand-in in cpp/mlx) and its test program
+"""Build the C++ layer: lib/libmlxr_primitives.so (MLXR's Primitive classes and free functions
+and the graph layers RMSNorm / Linear / RotaryEmbedding / MLP over the C ABI, compiled against
+the MLX stand-in in cpp/mlx) and its test program
 lib/primitives_test.  Plain g++; the CUDA runtime is needed for managed memory and streams.
 
     python -m mlxr_b200.build_cpp
@@ -45,7 +46,8 @@ def build(force: bool = False):
     from . import build as cuda_build
     core = cuda_build.build()
     os.makedirs(OUT, exist_ok=True)
-    srcs = [os.path.join(CPP, "mlx_shim.cpp"), os.path.join(CPP, "primitives", "mlxr_kernels.cpp")]
+    srcs = [os.path.join(CPP, "mlx_shim.cpp"), os.path.join(CPP, "primitives", "mlxr_kernels.cpp"),
+            os.path.join(CPP, "graph", "layers.cpp")]
     deps = _tree(CPP) + [os.path.join(os.path.dirname(HERE), "include", "mlxr_b200.h"), core]
     link = [f"-L{OUT}", "-lmlxr_b200", f"-L{CUDA}/lib64", "-lcudart", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{CUDA}/lib64"]
     if force or _newer(LIB, deps):

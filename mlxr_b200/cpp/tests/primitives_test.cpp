@@ -17,9 +17,11 @@
 #include "rmsnorm_primitive.h"
 #include "rope_apply_primitive.h"
 #include "swiglu_mlp_primitive.h"
+#include "../graph/layers.h"
 
 namespace mx = mlx::core;
 using namespace mlxr::kernels;
+namespace gr = mlxr::graph;
 
 static int g_failed = 0, g_run = 0;
 #define CHECK(cond)                                                              \
@@ -219,7 +221,143 @@ TEST(no_cpu_path) {
   return ok;
 }
 
+// ---- graph layers (core/graph/layers.h): the reference's tests/unit/layers_test.cpp checks shapes
+// and finiteness only; these compare with host arithmetic as well -------------------------------
+TEST(graph_rmsnorm_and_dense_linear) {
+  bool ok = true;
+  const int B = 2, T = 3, H = 256, O = 96;
+  auto x = randn((size_t)B * T * H, 21);
+  gr::RMSNorm norm(H, 1e-5f);
+  CHECK(norm.weight().shape() == std::vector<int>({H}));
+  gr::Tensor xt = gr::from_data(x.data(), {B, T, H}, mx::float32);
+  auto y = to_host(norm.forward(xt).array());
+  std::vector<float> want(x.size());
+  for (int r = 0; r < B * T; r++) {
+    double ss = 0;
+    for (int i = 0; i < H; i++) ss += (double)x[r * H + i] * x[r * H + i];
+    const double inv = 1.0 / std::sqrt(ss / H + 1e-5);
+    for (int i = 0; i < H; i++) want[r * H + i] = (float)(x[r * H + i] * inv);   // weight initialised to ones (layers.cpp:26-29)
+  }
+  CHECK(rel_l2(y, want) < 1e-5);
+  gr::Linear lin(H, O, true);
+  CHECK(lin.weight().shape() == std::vector<int>({O, H}) && lin.bias() != nullptr);
+  auto w = randn((size_t)O * H, 22, 0.05f), b = randn(O, 23);
+  lin.weight() = gr::from_data(w.data(), {O, H}, mx::float32);
+  *lin.bias() = gr::from_data(b.data(), {O}, mx::float32);
+  gr::Tensor out = lin.forward(xt);
+  CHECK(out.shape() == std::vector<int>({B, T, O}));
+  auto got = to_host(out.array());
+  std::vector<float> wl((size_t)B * T * O);
+  for (int r = 0; r < B * T; r++)
+    for (int o = 0; o < O; o++) {
+      double s = b[o];
+      for (int i = 0; i < H; i++) s += (double)x[r * H + i] * w[(size_t)o * H + i];
+      wl[(size_t)r * O + o] = (float)s;
+    }
+  CHECK(rel_l2(got, wl) < 1e-5);
+  gr::Linear nob(H, O);
+  CHECK(nob.bias() == nullptr);
+  bool threw = false;
+  try { nob.forward(gr::zeros({2, H + 1})); } catch (const std::invalid_argument&) { threw = true; }
+  CHECK(threw);
+  return ok;
+}
+
+TEST(graph_rotary_embedding_split_half) {
+  bool ok = true;
+  const int B = 1, T = 5, heads = 2, d = 32, max_seq = 64, offset = 3;
+  gr::RotaryEmbedding rope(d, max_seq, 10000.0f);
+  CHECK(rope.cos_table().shape() == std::vector<int>({max_seq, d / 2}));
+  auto q = randn((size_t)B * T * heads * d, 31), k = randn((size_t)B * T * heads * d, 32);
+  auto out = rope.forward(gr::from_data(q.data(), {B, T, heads, d}, mx::float32), gr::from_data(k.data(), {B, T, heads, d}, mx::float32), offset);
+  auto gq = to_host(out.first.array()), gk = to_host(out.second.array());
+  std::vector<float> wq(q.size()), wk(k.size());
+  for (int t = 0; t < T; t++)
+    for (int h = 0; h < heads; h++)
+      for (int p = 0; p < d / 2; p++) {
+        const float freq = 1.0f / std::pow(10000.0f, (2.0f * p) / d);      // layers.cpp:126-129
+        const float ang = (float)(offset + t) * freq;
+        const float c = std::cos(ang), s = std::sin(ang);
+        const size_t o = ((size_t)t * heads + h) * d;
+        wq[o + p] = q[o + p] * c - q[o + d / 2 + p] * s;                     // rotate_half: layers.cpp:196-208
+        wq[o + d / 2 + p] = q[o + d / 2 + p] * c + q[o + p] * s;
+        wk[o + p] = k[o + p] * c - k[o + d / 2 + p] * s;
+        wk[o + d / 2 + p] = k[o + d / 2 + p] * c + k[o + p] * s;
+      }
+  CHECK(rel_l2(gq, wq) < 1e-6 && rel_l2(gk, wk) < 1e-6);
+  bool threw = false;
+  try { gr::RotaryEmbedding bad(7, 8); } catch (const std::invalid_argument&) { threw = true; }
+  CHECK(threw);                                       // layers.cpp:115-117
+  threw = false;
+  try { rope.forward(gr::zeros({T, heads, d}), gr::zeros({T, heads, d})); } catch (const std::invalid_argument&) { threw = true; }
+  CHECK(threw);                                       // layers.cpp:164-168
+  return ok;
+}
+
+TEST(graph_mlp_dense_and_quantized) {
+  bool ok = true;
+  const int M = 2, H = 512, I = 1024;
+  auto x = randn((size_t)M * H, 41);
+  gr::Tensor xt = gr::from_data(x.data(), {M, H}, mx::float32);
+  std::vector<uint8_t> pg, pu, pd;
+  std::vector<float> wg, wu, wd;
+  make_q4_0(I, H, 42, pg, wg);
+  make_q4_0(I, H, 43, pu, wu);
+  make_q4_0(H, I, 44, pd, wd);
+  // host expectation: down(SiLU(gate(n)) * up(n)), n = rmsnorm(x) with unit weight
+  std::vector<float> n(x.size()), hbuf((size_t)M * I), want((size_t)M * H);
+  for (int m = 0; m < M; m++) {
+    double ss = 0;
+    for (int i = 0; i < H; i++) ss += (double)x[m * H + i] * x[m * H + i];
+    const double inv = 1.0 / std::sqrt(ss / H + 1e-5);
+    for (int i = 0; i < H; i++) n[m * H + i] = (float)(x[m * H + i] * inv);
+    for (int i = 0; i < I; i++) {
+      double g = 0, u = 0;
+      for (int k = 0; k < H; k++) { g += (double)n[m * H + k] * wg[(size_t)i * H + k]; u += (double)n[m * H + k] * wu[(size_t)i * H + k]; }
+      hbuf[(size_t)m * I + i] = (float)(g / (1.0 + std::exp(-g)) * u);
+    }
+    for (int o = 0; o < H; o++) {
+      double s = 0;
+      for (int i = 0; i < I; i++) s += (double)hbuf[(size_t)m * I + i] * wd[(size_t)o * I + i];
+      want[(size_t)m * H + o] = (float)s;
+    }
+  }
+  gr::RMSNorm norm(H, 1e-5f);
+  // dense weights: three Linear::forward calls and swiglu (layers.cpp:400-420)
+  gr::MLP dense(H, I);
+  dense.gate_proj().weight() = gr::from_data(wg.data(), {I, H}, mx::float32);
+  dense.up_proj().weight() = gr::from_data(wu.data(), {I, H}, mx::float32);
+  dense.down_proj().weight() = gr::from_data(wd.data(), {H, I}, mx::float32);
+  auto got_dense = to_host(dense.forward(norm.forward(xt)).array());
+  CHECK(rel_l2(got_dense, want) < 1e-4);
+  // packed weights: the fused block, with the RMSNorm prologue inside the same call
+  gr::MLP q(H, I);
+  q.gate_proj().set_quantized(gr::from_data(pg.data(), {(int)pg.size()}, mx::uint8), QuantType::Q4_0);
+  q.up_proj().set_quantized(gr::from_data(pu.data(), {(int)pu.size()}, mx::uint8), QuantType::Q4_0);
+  q.down_proj().set_quantized(gr::from_data(pd.data(), {(int)pd.size()}, mx::uint8), QuantType::Q4_0);
+  gr::Tensor yq = q.forward(xt, norm);
+  CHECK(yq.shape() == std::vector<int>({M, H}));
+  CHECK(rel_l2(to_host(yq.array()), want) < 2e-3);
+  // a single quantized Linear
+  auto yl = to_host(q.gate_proj().forward(gr::from_data(n.data(), {M, H}, mx::float32)).array());
+  std::vector<float> wlg((size_t)M * I);
+  for (int m = 0; m < M; m++)
+    for (int i = 0; i < I; i++) {
+      double g = 0;
+      for (int k = 0; k < H; k++) g += (double)n[m * H + k] * wg[(size_t)i * H + k];
+      wlg[(size_t)m * I + i] = (float)g;
+    }
+  CHECK(rel_l2(yl, wlg) < 1e-3);
+  bool threw = false;
+  try { q.gate_proj().set_quantized(gr::zeros({10}, mx::uint8), QuantType::Q4_0); } catch (const std::invalid_argument&) { threw = true; }
+  CHECK(threw);
+  return ok;
+}
+
 int main() {
+  RUN(graph_rmsnorm_and_dense_linear);
+  RUN(graph_rotary_embedding_split_half);
+  RUN(graph_mlp_dense_and_quantized);
   RUN(rmsnorm_matches_formula);
   RUN(rmsnorm_rejects_bad_weight);
   RUN(q_gemm_matches_dequantized_matmul);

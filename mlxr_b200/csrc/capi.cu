@@ -120,7 +120,7 @@ static int check_quant(int qt, int K, int group_size, bool check_group) {
     return MLXR_ERR_SHAPE;
   }
   if (check_group) {
-    const bool kq = (qt == MLXR_Q4_K);
+    const bool kq = (qt == MLXR_Q4_K || qt == MLXR_GGML_Q4_K);
     if (!(group_size == be || (kq && group_size == 32))) {
       set_error("group_size %d does not match format %s (block %d%s)", group_size,
                 mlxr_quant_type_name(qt), be, kq ? ", or 32" : "");
@@ -223,6 +223,8 @@ int mlxr_default_group_size(int qt) {
 const char* mlxr_quant_type_name(int qt) {
   static const char* names[] = {"Q4_0", "Q4_1", "Q8_0", "Q4_K", "Q6_K", "Q5_0", "Q5_1", "Q8_1", "Q2_K",
                                 "Q3_K", "Q5_K", "Q8_K", "IQ2_XXS", "IQ2_XS", "IQ3_XXS", "IQ3_S", "NF4"};
+  if (qt == MLXR_GGML_Q4_0) return "GGML_Q4_0";
+  if (qt == MLXR_GGML_Q4_K) return "GGML_Q4_K";
   return (qt >= 0 && qt <= 16) ? names[qt] : "Unknown";
 }
 const char* mlxr_rope_scaling_mode_name(int mode) {
@@ -352,6 +354,53 @@ int mlxr_rope_apply(const void* x, const uint16_t* cos_f16, const uint16_t* sin_
     }
   }
   return MLXR_OK;
+}
+
+int mlxr_repack_ggml_q4_0(const void* ggml_blocks, void* mlxr_blocks, int N, int K, void* stream) {
+  if (N < 0 || K < 0 || K % 32 != 0) { set_error("K = %d must be a multiple of the Q4_0 block size 32", K); return MLXR_ERR_SHAPE; }
+  const size_t nblocks = (size_t)N * (size_t)(K / 32);
+  if (nblocks == 0) return MLXR_OK;
+  if (!ggml_blocks || !mlxr_blocks) { set_error("null pointer"); return MLXR_ERR_INVALID_ARGUMENT; }
+  if (((uintptr_t)ggml_blocks & 1u) || ((uintptr_t)mlxr_blocks & 1u)) { set_error("block buffers must be 2-byte aligned"); return MLXR_ERR_INVALID_ARGUMENT; }
+  return launch_repack_ggml_q4_0(ggml_blocks, mlxr_blocks, nblocks, (cudaStream_t)stream);
+}
+
+int mlxr_rope_tables_f32_host(float* cos_f32, float* sin_f32, int max_seq_len, int dim, float base) {
+  if (!cos_f32 || !sin_f32) { set_error("null table pointer"); return MLXR_ERR_INVALID_ARGUMENT; }
+  if (dim <= 0 || dim % 2 != 0) { set_error("RotaryEmbedding dimension must be even"); return MLXR_ERR_INVALID_ARGUMENT; }
+  if (max_seq_len < 0) { set_error("max_seq_len must be >= 0"); return MLXR_ERR_SHAPE; }
+  const int half = dim / 2;
+  for (int pos = 0; pos < max_seq_len; pos++)
+    for (int i = 0; i < half; i++) {
+      const float freq = 1.0f / std::pow(base, (2.0f * i) / dim);
+      const float angle = (float)pos * freq;
+      cos_f32[(size_t)pos * half + i] = std::cos(angle);
+      sin_f32[(size_t)pos * half + i] = std::sin(angle);
+    }
+  return MLXR_OK;
+}
+
+int mlxr_rope_apply_split_half(const void* x, const float* cos_f32, const float* sin_f32, void* y, int batch, int seq,
+                               int heads, int head_dim, int max_seq_len, int offset, int dtype, void* stream) {
+  if (int r = check_dtype(dtype)) return r;
+  if (head_dim <= 0 || head_dim % 2 != 0) { set_error("RotaryEmbedding dimension must be even"); return MLXR_ERR_INVALID_ARGUMENT; }
+  if (batch < 0 || seq < 0 || heads < 0 || max_seq_len < 0) { set_error("negative dimension"); return MLXR_ERR_SHAPE; }
+  if (offset < 0 || (long long)offset + seq > max_seq_len) {
+    set_error("positions %d .. %d lie outside the table of %d rows", offset, offset + seq, max_seq_len);
+    return MLXR_ERR_SHAPE;
+  }
+  if ((size_t)batch * seq * heads == 0) return MLXR_OK;
+  if (!x || !y || !cos_f32 || !sin_f32) { set_error("null pointer"); return MLXR_ERR_INVALID_ARGUMENT; }
+  return launch_rope_split_half(x, cos_f32, sin_f32, y, (size_t)batch, seq, heads, head_dim, offset, dtype, (cudaStream_t)stream);
+}
+
+int mlxr_linear_dense(const void* x, const void* weight, const void* bias, void* y, int M, int N, int K, int dtype,
+                      void* stream) {
+  if (int r = check_dtype(dtype)) return r;
+  if (M < 0 || N < 0 || K <= 0) { set_error("Linear: bad dimensions M=%d N=%d K=%d", M, N, K); return MLXR_ERR_SHAPE; }
+  if (M == 0 || N == 0) return MLXR_OK;
+  if (!x || !weight || !y) { set_error("null pointer"); return MLXR_ERR_INVALID_ARGUMENT; }
+  return launch_linear_dense(x, weight, bias, y, M, N, K, dtype, (cudaStream_t)stream);
 }
 
 // y_f32: y is float [M, hidden] and receives the unrounded sums (a rank's partial result of a

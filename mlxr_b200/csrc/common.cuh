@@ -33,16 +33,16 @@ void count_launch(int n = 1);
 // Elements and bytes per block; 0 for a format without code.
 __host__ __device__ inline int block_elems(int qt) {
   switch (qt) {
-    case MLXR_Q4_0: case MLXR_Q4_1: case MLXR_Q8_0: return 32;
-    case MLXR_Q4_K: return 256;
+    case MLXR_Q4_0: case MLXR_Q4_1: case MLXR_Q8_0: case MLXR_GGML_Q4_0: return 32;
+    case MLXR_Q4_K: case MLXR_GGML_Q4_K: return 256;
     case MLXR_NF4: return 64;
     default: return 0;
   }
 }
 __host__ __device__ inline int block_bytes(int qt) {
   switch (qt) {
-    case MLXR_Q4_0: return 18; case MLXR_Q4_1: return 20; case MLXR_Q8_0: return 34;
-    case MLXR_Q4_K: return 144; case MLXR_NF4: return 34;
+    case MLXR_Q4_0: case MLXR_GGML_Q4_0: return 18; case MLXR_Q4_1: return 20; case MLXR_Q8_0: return 34;
+    case MLXR_Q4_K: case MLXR_GGML_Q4_K: return 144; case MLXR_NF4: return 34;
     default: return 0;
   }
 }
@@ -177,6 +177,46 @@ __device__ __forceinline__ void dequant_unit(const uint8_t* __restrict__ row, in
       w[4 * i + 2] = kNF4[(v >> 8) & 15u] * a;
       w[4 * i + 3] = kNF4[(v >> 12) & 15u] * a;
     }
+  } else if constexpr (QT == MLXR_GGML_Q4_0) {
+    // canonical ggml block: element i = low nibble of qs[i], element i + 16 = high nibble;
+    // w = (q - 8) * d, exact in fp32 (gguf.quants Q4_0.dequantize_blocks)
+    const uint8_t* b = row + (size_t)u * 18;
+    const float s = __half2float(h_from_bits(ld_u16(b)));
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const uint32_t v = ld_u16(b + 2 + 2 * i);
+      w[2 * i + 0] = (float)((int)(v & 15u) - 8) * s;
+      w[2 * i + 1] = (float)((int)((v >> 8) & 15u) - 8) * s;
+      w[2 * i + 16] = (float)((int)((v >> 4) & 15u) - 8) * s;
+      w[2 * i + 17] = (float)((int)((v >> 12) & 15u) - 8) * s;
+    }
+  } else if constexpr (QT == MLXR_GGML_Q4_K) {
+    // canonical ggml super-block: sub-block s of 64-element chunk j = s / 2 takes the low (s even)
+    // or high (s odd) nibbles of qs[32j .. 32j+31]; eight independent 6-bit (scale, min) pairs in
+    // the get_scale_min_k4 packing; w = (d * sc) * q - dmin * m with every float32 operation
+    // rounded on its own (gguf.quants Q4_K.dequantize_blocks; the products are exact)
+    const uint8_t* b = row + (size_t)(u >> 3) * 144;
+    const int s = u & 7;
+    const float d = __half2float(h_from_bits(ld_u16(b))), dmin = __half2float(h_from_bits(ld_u16(b + 2)));
+    uint8_t sc12[12];
+#pragma unroll
+    for (int i = 0; i < 6; i++) {
+      const uint32_t v = ld_u16(b + 4 + 2 * i);
+      sc12[2 * i] = (uint8_t)(v & 0xFFu);
+      sc12[2 * i + 1] = (uint8_t)(v >> 8);
+    }
+    int sc, mn;
+    if (s < 4) { sc = sc12[s] & 63; mn = sc12[s + 4] & 63; }
+    else { sc = (sc12[s + 4] & 0x0F) | ((sc12[s - 4] >> 6) << 4); mn = (sc12[s + 4] >> 4) | ((sc12[s] >> 6) << 4); }
+    const float ds = __fmul_rn(d, (float)sc), dm = __fmul_rn(dmin, (float)mn);
+    const uint8_t* q = b + 16 + 32 * (s >> 1);
+    const int shift = (s & 1) * 4;
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+      const uint32_t v = ld_u16(q + 2 * i);
+      w[2 * i + 0] = __fsub_rn(__fmul_rn(ds, (float)((v >> shift) & 15u)), dm);
+      w[2 * i + 1] = __fsub_rn(__fmul_rn(ds, (float)((v >> (8 + shift)) & 15u)), dm);
+    }
   } else if constexpr (QT == MLXR_Q4_K) {
     const uint8_t* b = row + (size_t)(u >> 3) * 144;
     const int s = u & 7;
@@ -214,6 +254,8 @@ __device__ __forceinline__ void dequant_unit(const uint8_t* __restrict__ row, in
     case MLXR_Q8_0: { constexpr int QT = MLXR_Q8_0; __VA_ARGS__; break; }           \
     case MLXR_Q4_K: { constexpr int QT = MLXR_Q4_K; __VA_ARGS__; break; }           \
     case MLXR_NF4: { constexpr int QT = MLXR_NF4; __VA_ARGS__; break; }             \
+    case MLXR_GGML_Q4_0: { constexpr int QT = MLXR_GGML_Q4_0; __VA_ARGS__; break; } \
+    case MLXR_GGML_Q4_K: { constexpr int QT = MLXR_GGML_Q4_K; __VA_ARGS__; break; } \
     default: ::mlxr::set_error("quant type %d has no implementation", (int)(qt));   \
              return MLXR_ERR_UNSUPPORTED;                                           \
   }

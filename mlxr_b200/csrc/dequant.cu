@@ -45,6 +45,36 @@ __global__ void __launch_bounds__(256) dequantize_kernel(const uint8_t* __restri
   }
 }
 
+// Canonical ggml Q4_0 -> MLXR Q4_0: one thread per block; element i (low nibble of qs[i]) and
+// element i + 16 (high nibble) go to byte i/2 / (i+16)/2 as the low (even element) or high nibble.
+__global__ void __launch_bounds__(256) repack_ggml_q4_0_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, size_t nblocks) {
+  for (size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x; b < nblocks; b += (size_t)gridDim.x * blockDim.x) {
+    const uint8_t* s = src + b * 18;
+    uint8_t* d = dst + b * 18;
+    uint8_t q[16];
+#pragma unroll
+    for (int i = 0; i < 8; i++) { const uint32_t v = ld_u16(s + 2 + 2 * i); q[2 * i] = (uint8_t)(v & 0xFFu); q[2 * i + 1] = (uint8_t)(v >> 8); }
+    *reinterpret_cast<uint16_t*>(d) = ld_u16(s);
+    uint8_t o[16];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      o[i] = (uint8_t)((q[2 * i] & 0x0F) | ((q[2 * i + 1] & 0x0F) << 4));          // elements 2i, 2i+1 (< 16): low nibbles
+      o[8 + i] = (uint8_t)((q[2 * i] >> 4) | ((q[2 * i + 1] >> 4) << 4));          // elements 16+2i, 17+2i: high nibbles
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) *reinterpret_cast<uint16_t*>(d + 2 + 2 * i) = (uint16_t)(o[2 * i] | (o[2 * i + 1] << 8));
+  }
+}
+
+int launch_repack_ggml_q4_0(const void* src, void* dst, size_t nblocks, cudaStream_t st) {
+  if (nblocks == 0) return MLXR_OK;
+  size_t blocks = (nblocks + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  repack_ggml_q4_0_kernel<<<(int)blocks, 256, 0, st>>>((const uint8_t*)src, (uint8_t*)dst, nblocks);
+  MLXR_LAUNCH_CHECK("repack_ggml_q4_0_kernel");
+  return MLXR_OK;
+}
+
 int launch_dequantize(const void* w, void* out, int N, int K, int qt, int out_dtype, int flags,
                       cudaStream_t st) {
   const int units = K / 32;

@@ -174,4 +174,43 @@ int launch_rope(const void* x, const uint16_t* cos_t, const uint16_t* sin_t,
   return MLXR_OK;
 }
 
+// ---- RoPE, split-half convention --------------------------------------------------------
+// graph::RotaryEmbedding::forward (core/graph/layers.cpp:157-225): the head is split in two
+// halves (x1 = first d/2 elements, x2 = the rest), positions are the contiguous range
+// offset .. offset + seq, tables are float32 [max_seq, d/2]:
+//   y1 = x1 * cos - x2 * sin,  y2 = x2 * cos + x1 * sin
+// as four products and two sums, each rounded to float32 (the composition materialises every
+// product as an array); one rounding to T at the store.  One thread per (token, head, p).
+template <typename T>
+__global__ void __launch_bounds__(256) rope_split_half_kernel(const T* __restrict__ x, const float* __restrict__ cos_t,
+                                                              const float* __restrict__ sin_t, T* __restrict__ y,
+                                                              size_t batch, int seq, int heads, int half, int offset) {
+  const size_t total = batch * seq * heads * half;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int p = (int)(i % half);
+    const size_t th = i / half;            // (batch * seq + t) * heads + head
+    const int t = (int)((th / heads) % seq);
+    const size_t tab = (size_t)(offset + t) * half + p;
+    const float c = cos_t[tab], sn = sin_t[tab];
+    const size_t e = th * (size_t)(2 * half) + p;
+    const float x1 = Act<T>::to_f(x[e]), x2 = Act<T>::to_f(x[e + half]);
+    y[e] = Act<T>::from_f(__fsub_rn(__fmul_rn(x1, c), __fmul_rn(x2, sn)));
+    y[e + half] = Act<T>::from_f(__fadd_rn(__fmul_rn(x2, c), __fmul_rn(x1, sn)));
+  }
+}
+
+int launch_rope_split_half(const void* x, const float* cos_t, const float* sin_t, void* y, size_t batch, int seq,
+                           int heads, int head_dim, int offset, int dtype, cudaStream_t st) {
+  const size_t total = batch * seq * heads * (head_dim / 2);
+  if (total == 0) return MLXR_OK;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  MLXR_DISPATCH_DTYPE(dtype, T, {
+    rope_split_half_kernel<T><<<(int)blocks, 256, 0, st>>>((const T*)x, cos_t, sin_t, (T*)y, batch, seq, heads,
+                                                           head_dim / 2, offset);
+  });
+  MLXR_LAUNCH_CHECK("rope_split_half_kernel");
+  return MLXR_OK;
+}
+
 }  // namespace mlxr

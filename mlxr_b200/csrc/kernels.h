@@ -12,6 +12,7 @@ constexpr int kSyncWords = 4096;
 
 int launch_dequantize(const void* w, void* out, int N, int K, int qt, int out_dtype, int flags,
                       cudaStream_t st);
+int launch_repack_ggml_q4_0(const void* src, void* dst, size_t nblocks, cudaStream_t st);
 int launch_qgemm_generic(const void* x, const void* w, const void* bias, void* y, int M, int N,
                          int K, int qt, int dtype, cudaStream_t st);
 bool gemv_rows_supported(int qt, int M, int K, const void* x, const void* w);
@@ -30,6 +31,9 @@ int launch_rope(const void* x, const uint16_t* cos_t, const uint16_t* sin_t,
                 const int32_t* positions, void* y, size_t tokens, int heads, int head_dim,
                 int max_seq, int mode, float scale, int offset, int dtype, int* status,
                 cudaStream_t st);
+
+int launch_rope_split_half(const void* x, const float* cos_t, const float* sin_t, void* y, size_t batch, int seq,
+                           int heads, int head_dim, int offset, int dtype, cudaStream_t st);
 
 // ---- exchange buffer of the tensor-parallel block (tp.cu, decode_kernel.cuh) -------------------
 // One per rank, mapped by every peer:

@@ -13,7 +13,10 @@ reason (daemon/server/model_loader.cpp:236-245).  This module is the missing ste
   allow_requantize=True)` dequantizes with gguf.quants and re-quantizes into MLXR's Q4_K
   (lossy; the result says so).
 
-Nothing here runs on the GPU or in the hot path.
+The device side can also read the canonical layouts directly (QuantType.GGML_Q4_0 /
+GGML_Q4_K: bit-exact dequantization and the generic quantized linear) and repack canonical Q4_0
+into MLXR's Q4_0 on the GPU (ops.repack_ggml_q4_0); `load_linear_raw` hands a tensor's bytes over
+unchanged for that.  Nothing in this module runs on the GPU or in the hot path.
 """
 from __future__ import annotations
 
@@ -71,6 +74,25 @@ def convert(raw: np.ndarray, N: int, K: int, ggml_type: int, allow_requantize: b
     from .quantize import quantize
     w = gq.dequantize(raw.reshape(N, -1), GGMLQuantizationType(ggml_type)).astype(np.float32).reshape(N, K)
     return Converted(quantize(w, int(QuantType.Q4_K)), QuantType.Q4_K, False)
+
+
+def load_linear_raw(path: str, name: str) -> Tuple[np.ndarray, QuantType, int, int]:
+    """Read tensor `name` ([N, K]) from a .gguf file WITHOUT conversion: its bytes as stored, the
+    canonical-layout quant type the device kernels take for them, N and K."""
+    from gguf import GGUFReader
+    reader = GGUFReader(path)
+    native = {GGML_Q4_0: QuantType.GGML_Q4_0, GGML_Q4_K: QuantType.GGML_Q4_K, GGML_Q8_0: QuantType.Q8_0}
+    for t in reader.tensors:
+        if t.name == name:
+            shape = [int(d) for d in t.shape]          # GGUF stores dimensions innermost first
+            if len(shape) != 2:
+                raise ValueError(f"{name} is not a matrix (shape {shape})")
+            K, N = shape
+            gt = int(t.tensor_type)
+            if gt not in native:
+                raise ValueError(f"GGML type {gt} has no device-side layout")
+            return np.ascontiguousarray(np.asarray(t.data)).view(np.uint8).reshape(-1).copy(), native[gt], N, K
+    raise KeyError(name)
 
 
 def load_linear(path: str, name: str, allow_requantize: bool = False) -> Tuple[Converted, int, int]:

@@ -89,6 +89,13 @@ def dequantize(weights: torch.Tensor, N: int, K: int, quant_type: QuantType,
     return out
 
 
+def repack_ggml_q4_0(ggml_blocks: torch.Tensor, N: int, K: int) -> torch.Tensor:
+    """Canonical ggml Q4_0 blocks [N, K] (device, uint8) -> MLXR Q4_0 blocks: value-preserving."""
+    out = torch.empty_like(ggml_blocks)
+    check(lib.mlxr_repack_ggml_q4_0(_dev(ggml_blocks, "ggml_blocks"), out.data_ptr(), N, K, _stream()))
+    return out
+
+
 def q_gemm_dequant(input: torch.Tensor, weights: torch.Tensor, M: int, N: int, K: int,
                    quant_type: QuantType, group_size: int, bias: Optional[torch.Tensor] = None
                    ) -> torch.Tensor:
@@ -210,6 +217,64 @@ def rope_apply(input: torch.Tensor, cos_table: torch.Tensor, sin_table: torch.Te
                               cos_table.shape[0], int(scaling_mode), scale_factor, position_offset,
                               _dtype_code(input), 1 if check_positions else 0, _stream()))
     return out
+
+
+class RotaryEmbedding:
+    """graph::RotaryEmbedding (core/graph/layers.h:67-90, layers.cpp:113-225): the split-half
+    ("rotate_half") convention with float32 tables and contiguous positions offset .. offset + seq -
+    not the interleaved convention of rope_apply above (the reference has both)."""
+
+    def __init__(self, dim: int, max_seq_len: int, base: float = 10000.0):
+        if dim % 2 != 0:
+            raise _capi.MlxrInvalidArgument(_capi.ERR_INVALID_ARGUMENT, "RotaryEmbedding dimension must be even")
+        self.dim, self.max_seq_len, self.base = dim, max_seq_len, base
+        cos = torch.empty((max_seq_len, dim // 2), dtype=torch.float32)
+        sin = torch.empty_like(cos)
+        check(lib.mlxr_rope_tables_f32_host(cos.data_ptr(), sin.data_ptr(), max_seq_len, dim, base))
+        self.cos_host, self.sin_host = cos, sin
+        self._dev = {}
+
+    def cos_table(self) -> torch.Tensor:
+        return self.cos_host
+
+    def sin_table(self) -> torch.Tensor:
+        return self.sin_host
+
+    def _tables(self, device):
+        if device not in self._dev:
+            self._dev[device] = (self.cos_host.to(device), self.sin_host.to(device))
+        return self._dev[device]
+
+    def forward(self, q: torch.Tensor, k: torch.Tensor, offset: int = 0):
+        """q, k: [batch, seq_len, num_heads, head_dim] -> (q_rotated, k_rotated)."""
+        if q.dim() != 4 or k.dim() != 4:
+            raise _capi.MlxrInvalidArgument(_capi.ERR_INVALID_ARGUMENT,
+                                            "RotaryEmbedding expects 4D tensors [batch, seq_len, num_heads, head_dim]")
+        if q.shape[3] != self.dim or k.shape[3] != self.dim:
+            raise _capi.MlxrInvalidArgument(_capi.ERR_INVALID_ARGUMENT, "head_dim must match RotaryEmbedding dim")
+        outs = []
+        for t in (q, k):
+            cos, sin = self._tables(t.device)
+            out = torch.empty_like(t)
+            b, sq, h, d = t.shape
+            check(lib.mlxr_rope_apply_split_half(_dev(t, "input"), cos.data_ptr(), sin.data_ptr(), out.data_ptr(), b, sq, h, d,
+                                                 self.max_seq_len, offset, _dtype_code(t), _stream()))
+            outs.append(out)
+        return outs[0], outs[1]
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """graph::Linear::forward (core/graph/layers.cpp:86-99) with a dense weight [out, in] of the
+    activation dtype: x[..., in] -> [..., out]."""
+    K = x.shape[-1]
+    N = weight.shape[0]
+    if weight.dim() != 2 or weight.shape[1] != K or weight.dtype != x.dtype:
+        raise _capi.MlxrError(_capi.ERR_SHAPE, "Linear: weight must be [out_features, in_features] of the input dtype")
+    M = x.numel() // K
+    y = torch.empty(x.shape[:-1] + (N,), dtype=x.dtype, device=x.device)
+    check(lib.mlxr_linear_dense(_dev(x, "input"), _dev(weight, "weight"), _dev(bias, "bias"), y.data_ptr(), M, N, K,
+                                _dtype_code(x), _stream()))
+    return y
 
 
 def mlp_block(x: torch.Tensor, norm_weight: Optional[torch.Tensor], w_gate: torch.Tensor,

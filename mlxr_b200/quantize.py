@@ -15,7 +15,7 @@ import numpy as np
 
 from .types import QuantType
 
-# the 16 NF4 levels: same construction as oracle/nf4_codebook.py
+# the 16 NF4 levels: the table the CUDA kernels include (csrc/nf4_codebook.inc)
 _NF4 = None
 
 
@@ -23,8 +23,7 @@ def nf4_levels() -> np.ndarray:
     global _NF4
     if _NF4 is None:
         import os
-        path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle",
-                            "nf4_codebook.inc")
+        path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc", "nf4_codebook.inc")
         vals = []
         with open(path) as f:
             for line in f:

@@ -21,6 +21,9 @@ class QuantType(IntEnum):
     IQ3_XXS = 14
     IQ3_S = 15
     NF4 = 16
+    # extension: canonical ggml layouts as stored in .gguf files (include/mlxr_b200.h)
+    GGML_Q4_0 = 32
+    GGML_Q4_K = 33
 
 
 class RoPEScalingMode(IntEnum):
@@ -38,4 +41,6 @@ BLOCK = {
     QuantType.Q8_0: (32, 34),
     QuantType.Q4_K: (256, 144),
     QuantType.NF4: (64, 34),
+    QuantType.GGML_Q4_0: (32, 18),
+    QuantType.GGML_Q4_K: (256, 144),
 }

@@ -430,6 +430,41 @@ ORC_API void orc_rope_apply(const float* x, const float* cos_t, const float* sin
     }
 }
 
+/* RoPE of the graph layer: graph::RotaryEmbedding, core/graph/layers.cpp:113-225 ("parity
+ * unpinned" beyond elementary IEEE arithmetic: the composition is made of MLX ops, and MLX is an
+ * absent third-party dependency).  compute_freqs (:121-154): freq_i = 1 / pow(base, 2i/dim),
+ * angle = pos * freq_i, float32 tables [max_seq, dim/2].  forward (:157-225): the head splits
+ * into halves x1 | x2, positions are offset .. offset + seq,
+ *   y1 = x1*cos - x2*sin;  y2 = x2*cos + x1*sin
+ * where every product and every sum is a separately materialised float32 array (built without
+ * contraction: the Makefile passes -ffp-contract=off). */
+ORC_API void orc_rope_tables_f32(int max_seq, int dim, float base, float* cos_f, float* sin_f) {
+  int half = dim / 2;
+  for (int pos = 0; pos < max_seq; pos++)
+    for (int i = 0; i < half; i++) {
+      float freq = 1.0f / powf(base, (2.0f * i) / dim);
+      float angle = (float)pos * freq;
+      cos_f[(size_t)pos * half + i] = cosf(angle);
+      sin_f[(size_t)pos * half + i] = sinf(angle);
+    }
+}
+ORC_API void orc_rope_split_half(const float* x, const float* cos_t, const float* sin_t, float* y,
+                                 int batch, int seq, int heads, int head_dim, int offset) {
+  int half = head_dim / 2;
+  for (int b = 0; b < batch; b++)
+    for (int t = 0; t < seq; t++)
+      for (int h = 0; h < heads; h++) {
+        size_t off = (((size_t)b * seq + t) * heads + h) * head_dim;
+        for (int p = 0; p < half; p++) {
+          float x1 = x[off + p], x2 = x[off + half + p];
+          float c = cos_t[(size_t)(offset + t) * half + p], s = sin_t[(size_t)(offset + t) * half + p];
+          float x1c = x1 * c, x2s = x2 * s, x2c = x2 * c, x1s = x1 * s;
+          y[off + p] = x1c - x2s;
+          y[off + half + p] = x2c + x1s;
+        }
+      }
+}
+
 /* In-place rounding of an fp32 buffer to the activation dtype and back (0 fp16, 1 bf16,
  * anything else: unchanged): marks the points where the composition materialises an
  * fp16/bf16 array. */

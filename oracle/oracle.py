@@ -56,6 +56,10 @@ def _load() -> C.CDLL:
     lib.orc_rope_tables.argtypes = [i, i, f, i, f, vp, vp, vp, vp]
     lib.orc_rope_apply.restype = None
     lib.orc_rope_apply.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, f, i]
+    lib.orc_rope_tables_f32.restype = None
+    lib.orc_rope_tables_f32.argtypes = [i, i, f, vp, vp]
+    lib.orc_rope_split_half.restype = None
+    lib.orc_rope_split_half.argtypes = [vp, vp, vp, vp, i, i, i, i, i]
     lib.orc_round_to.restype = None
     lib.orc_round_to.argtypes = [vp, sz, i]
     lib.orc_nf4_codebook.restype = C.POINTER(C.c_float)
@@ -151,6 +155,24 @@ def rope_apply(x: np.ndarray, cos_h: np.ndarray, sin_h: np.ndarray, positions: n
     y = np.empty_like(x)
     lib.orc_rope_apply(x.ctypes.data, cf.ctypes.data, sf.ctypes.data, pos.ctypes.data, y.ctypes.data,
                        batch, seq, heads, d, mode, scale, offset)
+    return y
+
+
+def rope_tables_f32(max_seq: int, dim: int, base: float = 10000.0):
+    """-> (cos, sin) float32 [max_seq, dim/2] as graph::RotaryEmbedding::compute_freqs builds them."""
+    c = np.empty((max_seq, dim // 2), dtype=np.float32)
+    s = np.empty_like(c)
+    lib.orc_rope_tables_f32(max_seq, dim, base, c.ctypes.data, s.ctypes.data)
+    return c, s
+
+
+def rope_split_half(x: np.ndarray, cos_f: np.ndarray, sin_f: np.ndarray, offset: int = 0) -> np.ndarray:
+    """x [batch, seq, heads, d] fp32; split-half rotation of graph::RotaryEmbedding::forward."""
+    x = _f32(x)
+    batch, seq, heads, d = x.shape
+    y = np.empty_like(x)
+    lib.orc_rope_split_half(x.ctypes.data, _f32(cos_f).ctypes.data, _f32(sin_f).ctypes.data, y.ctypes.data,
+                            batch, seq, heads, d, offset)
     return y
 
 

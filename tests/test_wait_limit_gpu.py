@@ -27,7 +27,7 @@ def _slot(buf, parity, src):
 
 
 def _flags(buf):
-    return buf[:FLAG_BYTES].view(torch.int32).view(MAX_WORLD, -1)[:, :FLAGS_PER_RANK]
+    return buf[:MAX_WORLD * FLAGS_PER_RANK * 4].view(torch.int32).view(MAX_WORLD, FLAGS_PER_RANK)
 
 
 def test_peer_wait_runs_out_then_recovers():
