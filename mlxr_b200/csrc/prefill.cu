@@ -20,6 +20,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstring>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -35,7 +36,12 @@ constexpr int kBN = 256;          // weight rows per tile (MMA N)
 constexpr int kBK = 64;           // K per stage: one 128-byte swizzle row of 16-bit elements
 constexpr int kUmmaK = 16;
 constexpr int kProducerWarps = 16; // one (weight row, 32-weight sub-block) per producer thread and stage
-constexpr int kThreads = (1 + kProducerWarps) * 32;
+constexpr int kThreads = (2 + kProducerWarps) * 32;   // MMA warp, producers, copy warp
+constexpr int kRawStages = 3;             // packed Q4_K nibbles staged by TMA: k-blocks in flight
+constexpr int kRawBytes = 2 * kBN * 16;   // per k-block: 256 rows x 16 bytes for each of the two sub-blocks
+constexpr int kHdrStages = 2;             // super-block headers (256 rows x 16 bytes) in flight
+constexpr int kHdrBytes = kBN * 16;
+constexpr int kRawRing = kRawStages * kRawBytes + kHdrStages * kHdrBytes;   // 32 KB
 constexpr int kATile = kBM * kBK * 2;     // 16 KB
 constexpr int kBTile = kBN * kBK * 2;     // 32 KB
 constexpr uint32_t kSpin = 1u << 22;
@@ -297,6 +303,8 @@ struct Shared {
   uint64_t full_a[4];
   uint64_t full_b[4];
   uint64_t empty[4];
+  uint64_t raw_full[kRawStages];    // the packed nibbles (and header) of a k-block have landed
+  uint64_t raw_empty[kRawStages];   // all producer warps have read them
   uint64_t acc_full;
   uint32_t tmem_base;
   int dead;
@@ -336,19 +344,26 @@ __device__ __forceinline__ void store_row(const Params& P, int m, int nc, const 
 
 // MT accumulators (MT x 128 rows of X) per CTA, STAGES pipeline stages.
 // Warp 0: tensor-memory owner and MMA issuer (lane 0).  Warps 1..16: producers; thread pp of them
-// owns (weight row pp & 255, sub-block pp >> 8 of the 64-wide k-block); the first of them also
-// issues the TMA copies of the X tiles, since it waits for the stage to be free anyway.
+// owns (weight row pp & 255, sub-block pp >> 8 of the 64-wide k-block).  Warp 17: copies (lane 0):
+// the X tiles and, for Q4_K, the packed weights, which reach the producers through a small
+// shared-memory ring filled by TMA boxes of 256 rows x 16 bytes (a thread's 16 bytes of nibbles
+// sit 2304 or 8064 bytes from its neighbour's in global memory: fetched by the threads
+// themselves, every warp-level load touched 32 different sectors and the producers waited on
+// them; the TMA unit walks the rows instead and the producers read dense shared memory).
 template <int QT, typename T, int MT, int STAGES, int BF>
 __global__ void __launch_bounds__(kThreads, 1)
-qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
+qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const Params P) {
   extern __shared__ uint8_t smem_raw[];
   // tiles need 1024-byte alignment for the 128-byte swizzle
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw & 1023u)) & 1023u;
   uint8_t* smem = smem_raw + pad;
   constexpr int kStageBytes = MT * kATile + kBTile;
-  Shared* sh = reinterpret_cast<Shared*>(smem + (size_t)STAGES * kStageBytes);
+  uint8_t* rawring = smem + (size_t)STAGES * kStageBytes;          // [kRawStages][2][256][16] then [kHdrStages][256][16]
+  uint8_t* hdrring = rawring + kRawStages * kRawBytes;
+  Shared* sh = reinterpret_cast<Shared*>(rawring + kRawRing);
   volatile int* dead = &sh->dead;
+  constexpr bool kStaged = (QT == MLXR_Q4_K);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * (MT * kBM);
   // this CTA's K-slice: k-blocks [kb0, kb0 + nkb)
@@ -364,6 +379,10 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
       mbar_init(smem_u32(&sh->full_a[s]), 1);
       mbar_init(smem_u32(&sh->full_b[s]), kProducerWarps);
       mbar_init(smem_u32(&sh->empty[s]), 1);
+    }
+    for (int r = 0; r < kRawStages; r++) {
+      mbar_init(smem_u32(&sh->raw_full[r]), 1);
+      mbar_init(smem_u32(&sh->raw_empty[r]), kProducerWarps);
     }
     mbar_init(smem_u32(&sh->acc_full), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -400,6 +419,48 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
       }
       if (ok) umma_commit(smem_u32(&sh->acc_full));
     }
+  } else if (warp == 1 + kProducerWarps) {
+    // ===== copies =====
+    if (lane == 0) {
+      int issued = 0;
+      for (int i = 0; i < nkb; i++) {
+        const int kb = kb0 + i;
+        if constexpr (kStaged) {
+          // packed nibbles of k-block kb (two boxes: sub-block 2 (kb % 4) and the next one), and the
+          // header of its super-block when a new one starts; x in 8-byte elements, always even
+          const int r = i % kRawStages, rit = i / kRawStages;
+          if (!mbar_wait(smem_u32(&sh->raw_empty[r]), (rit & 1) ^ 1, dead)) break;
+          const bool new_sb = (kb & 3) == 0 || i == 0;
+          const uint32_t bar = smem_u32(&sh->raw_full[r]);
+          mbar_expect_tx(bar, kRawBytes + (new_sb ? kHdrBytes : 0));
+          const int xq = 18 * (kb >> 2) + 2 + 4 * (kb & 3);
+          tma_load_2d(smem_u32(rawring + (size_t)r * kRawBytes), &wmap, xq, n0, bar);
+          tma_load_2d(smem_u32(rawring + (size_t)r * kRawBytes + kBN * 16), &wmap, xq + 2, n0, bar);
+          if (new_sb) tma_load_2d(smem_u32(hdrring + (size_t)((kb >> 2) & 1) * kHdrBytes), &wmap, 18 * (kb >> 2), n0, bar);
+        }
+        const int s = i % STAGES, it = i / STAGES;
+        if (!mbar_wait(smem_u32(&sh->empty[s]), (it & 1) ^ 1, dead)) break;
+        const uint32_t bar = smem_u32(&sh->full_a[s]);
+        mbar_expect_tx(bar, MT * kATile);
+#pragma unroll
+        for (int a = 0; a < MT; a++)
+          tma_load_2d(smem_u32(smem + (size_t)s * kStageBytes + a * kATile), &xmap, kb * kBK, m0 + a * kBM, bar);
+        issued = i + 1;
+      }
+      if (*dead) {
+        // copies in flight must land before the CTA may exit (bounded)
+        for (int j = max(0, issued - STAGES); j < issued; j++) {
+          const uint32_t bar = smem_u32(&sh->full_a[j % STAGES]);
+          for (uint32_t sp = 0; sp < kSpin; sp++) if (mbar_try(bar, (j / STAGES) & 1)) break;
+        }
+        if constexpr (kStaged) {
+          for (int j = max(0, issued - kRawStages); j < min(issued + 1, nkb); j++) {
+            const uint32_t bar = smem_u32(&sh->raw_full[j % kRawStages]);
+            for (uint32_t sp = 0; sp < kSpin; sp++) if (mbar_try(bar, (j / kRawStages) & 1)) break;
+          }
+        }
+      }
+    }
   } else {
     // ===== dequantizing producers =====
     const int pp = tid - 32;
@@ -407,7 +468,6 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     const int n = n0 + p;
     const bool live = n < P.N;
     const uint8_t* rowp = P.w + (size_t)(live ? n : 0) * P.row_bytes;
-    const bool tma_thread = (pp == 0);
     uint4 q0 = make_uint4(0, 0, 0, 0), q1 = q0, hdr = q0;
     // k-block kb: super-block kb / 4, this thread's sub-block s = 2 * (kb % 4) + hb (16 bytes of nibbles)
     auto fetch = [&](int kb, uint4& q) {
@@ -417,29 +477,22 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     };
     // nibbles are requested two k-blocks ahead (q0: even, q1: odd steps); the header of a
     // super-block arrives with its first k-block and is copied out before the next one overwrites it
-#ifdef MLXR_TUNING
-    const bool loads = live && !(P.debug & 2) && QT == MLXR_Q4_K;
-#else
-    const bool loads = live && QT == MLXR_Q4_K;
-#endif
+    (void)fetch; (void)q0; (void)q1;
     uint4 ch = make_uint4(0, 0, 0, 0);
-    if (loads) { fetch(kb0, q0); ch = hdr; if (nkb > 1) fetch(kb0 + 1, q1); }
-    int issued = 0;
     for (int i = 0; i < nkb; i++) {
       const int kb = kb0 + i;
       const int s = i % STAGES, it = i / STAGES;
-      const uint4 cq = (i & 1) ? q1 : q0;
-      if ((kb & 3) == 0 || i == 0) ch = hdr;
-      if (loads && i + 2 < nkb) { if (i & 1) fetch(kb + 2, q1); else fetch(kb + 2, q0); }
-      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->empty[s]), (it & 1) ^ 1, dead))) break;   // warp-uniform
-      if (tma_thread) {
-        const uint32_t bar = smem_u32(&sh->full_a[s]);
-        mbar_expect_tx(bar, MT * kATile);
-#pragma unroll
-        for (int a = 0; a < MT; a++)
-          tma_load_2d(smem_u32(smem + (size_t)s * kStageBytes + a * kATile), &xmap, kb * kBK, m0 + a * kBM, bar);
-        issued = i + 1;
+      uint4 cq = make_uint4(0, 0, 0, 0);
+      if constexpr (kStaged) {
+        // this thread's 16 bytes of nibbles and its row's header from the staged copies
+        const int r = i % kRawStages, rit = i / kRawStages;
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->raw_full[r]), rit & 1, dead))) break;   // warp-uniform
+        cq = *reinterpret_cast<const uint4*>(rawring + (size_t)r * kRawBytes + (size_t)hb * (kBN * 16) + (size_t)p * 16);
+        ch = *reinterpret_cast<const uint4*>(hdrring + (size_t)((kb >> 2) & 1) * kHdrBytes + (size_t)p * 16);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh->raw_empty[r]));
       }
+      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->empty[s]), (it & 1) ^ 1, dead))) break;   // warp-uniform
       uint8_t* brow = smem + (size_t)s * kStageBytes + MT * kATile + (size_t)p * 128;
       uint4 o[4];
 #ifdef MLXR_TUNING
@@ -487,13 +540,6 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sh->full_b[s]));
-    }
-    if (tma_thread && *dead) {
-      // copies in flight must land before the CTA may exit (bounded)
-      for (int j = max(0, issued - STAGES); j < issued; j++) {
-        const uint32_t bar = smem_u32(&sh->full_a[j % STAGES]);
-        for (uint32_t sp = 0; sp < kSpin; sp++) if (mbar_try(bar, (j / STAGES) & 1)) break;
-      }
     }
     __syncwarp();
     // ===== epilogue: warp (warp % 4) owns TMEM lanes 32 * (warp % 4) ..; the four producer
@@ -547,7 +593,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
       sh->last = last;
     }
     __syncthreads();
-    if (sh->last && warp >= 1) {
+    if (sh->last && warp >= 1 && warp <= kProducerWarps) {
       const int quarter = warp & 3, gi = (warp - 1) >> 2;
 #pragma unroll 1
       for (int u = gi; u < MT * (kBN / 32); u += 4) {
@@ -612,6 +658,24 @@ static int x_tensor_map(const void* x, int M, int K, int dtype, CUtensorMap* out
   return MLXR_OK;
 }
 
+// Packed Q4_K weights [N rows][row_bytes] as a 2-D tensor of 8-byte elements, boxes of 2 x 256
+// (16 bytes of 256 consecutive rows); rows past N read as zero.
+static int w_tensor_map(const void* w, int N, size_t row_bytes, CUtensorMap* out) {
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  MLXR_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+  if (!fn || q != cudaDriverEntryPointSuccess) { set_error("cuTensorMapEncodeTiled is not available in this driver"); return MLXR_ERR_CUDA; }
+  const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 8), (cuuint64_t)N};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {2, (cuuint32_t)prefill::kBN};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = ((EncodeTiledFn)fn)(out, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(w), dims, strides, box, estr,
+                                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%d) for W [%d rows of %zu bytes]", (int)r, N, row_bytes); return MLXR_ERR_CUDA; }
+  return MLXR_OK;
+}
+
 bool prefill_supported(int qt, int M, int N, int K, int dtype, const void* x, const void* w, const void* y) {
   if (dtype != MLXR_F16 && dtype != MLXR_BF16) return false;
   if (qt == MLXR_Q4_K) { if (K % 256 != 0 || (((uintptr_t)w) & 15u)) return false; }
@@ -623,10 +687,10 @@ bool prefill_supported(int qt, int M, int N, int K, int dtype, const void* x, co
 }
 
 template <int QT, typename T, int MT, int STAGES, int BF>
-static int launch_tc(const CUtensorMap& xmap, const prefill::Params& P, cudaStream_t st) {
+static int launch_tc(const CUtensorMap& xmap, const CUtensorMap& wmap, const prefill::Params& P, cudaStream_t st) {
   using namespace prefill;
   auto kern = qgemm_tc_kernel<QT, T, MT, STAGES, BF>;
-  constexpr size_t smem = (size_t)STAGES * (MT * kATile + kBTile) + sizeof(Shared) + 1024;
+  constexpr size_t smem = (size_t)STAGES * (MT * kATile + kBTile) + kRawRing + sizeof(Shared) + 1024;
   static bool attr_done[64] = {};
   int dev = 0;
   MLXR_CUDA_TRY(cudaGetDevice(&dev));
@@ -635,7 +699,7 @@ static int launch_tc(const CUtensorMap& xmap, const prefill::Params& P, cudaStre
     attr_done[dev & 63] = true;
   }
   dim3 grid((P.N + kBN - 1) / kBN, (P.M + MT * kBM - 1) / (MT * kBM), P.S);
-  kern<<<grid, kThreads, smem, st>>>(xmap, P);
+  kern<<<grid, kThreads, smem, st>>>(xmap, wmap, P);
   MLXR_LAUNCH_CHECK("qgemm_tc_kernel");
   return MLXR_OK;
 }
@@ -654,8 +718,12 @@ int prefill_slices(int M, int N, int K) {
 
 int launch_prefill(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int qt, int dtype,
                    int* status, float* partials, uint32_t* counters, int S, cudaStream_t st) {
-  CUtensorMap xmap;
+  CUtensorMap xmap, wmap;
   if (int r = x_tensor_map(x, M, K, dtype, &xmap)) return r;
+  memset(&wmap, 0, sizeof(wmap));
+  if (qt == MLXR_Q4_K) {
+    if (int r = w_tensor_map(w, N, (size_t)(K / 256) * 144, &wmap)) return r;
+  }
   prefill::Params P;
   P.w = (const uint8_t*)w;
   P.bias = bias;
@@ -675,8 +743,8 @@ int launch_prefill(const void* x, const void* w, const void* bias, void* y, int 
   int rc = MLXR_ERR_UNSUPPORTED;
 #define MLXR_TC_BY_QT(QTV)                                                                                     \
   do {                                                                                                         \
-    if (dtype == MLXR_F16) rc = two ? launch_tc<QTV, __half, 2, 3, 0>(xmap, P, st) : launch_tc<QTV, __half, 1, 4, 0>(xmap, P, st); \
-    else rc = two ? launch_tc<QTV, __nv_bfloat16, 2, 3, 1>(xmap, P, st) : launch_tc<QTV, __nv_bfloat16, 1, 4, 1>(xmap, P, st);     \
+    if (dtype == MLXR_F16) rc = two ? launch_tc<QTV, __half, 2, 3, 0>(xmap, wmap, P, st) : launch_tc<QTV, __half, 1, 4, 0>(xmap, wmap, P, st); \
+    else rc = two ? launch_tc<QTV, __nv_bfloat16, 2, 3, 1>(xmap, wmap, P, st) : launch_tc<QTV, __nv_bfloat16, 1, 4, 1>(xmap, wmap, P, st);     \
   } while (0)
   switch (qt) {
     case MLXR_Q4_K: MLXR_TC_BY_QT(MLXR_Q4_K); break;
