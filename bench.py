@@ -245,7 +245,7 @@ def timed_graph(step, K, W, stream, min_seconds=0.25, max_repeats=400, dist=None
         times = []
         total = 0.0
         t0 = time.perf_counter()
-        while total < min_seconds * 1e3 and len(times) < max_repeats:
+        while True:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(stream)
             graph.replay()
@@ -254,12 +254,14 @@ def timed_graph(step, K, W, stream, min_seconds=0.25, max_repeats=400, dist=None
             ms = e0.elapsed_time(e1)
             times.append(ms)
             total += ms
+            more = total < min_seconds * 1e3 and len(times) < max_repeats
             if dist is not None:
-                # all ranks leave the loop together (rank 0 decides)
-                flag = torch.tensor([1.0 if total < min_seconds * 1e3 and len(times) < max_repeats else 0.0], device="cuda")
+                # every rank replays the same number of times: rank 0 alone decides when to stop
+                flag = torch.tensor([1.0 if more else 0.0], device="cuda")
                 dist.broadcast(flag, 0)
-                if flag.item() == 0.0:
-                    break
+                more = flag.item() != 0.0
+            if not more:
+                break
         t1 = time.perf_counter()
     torch.cuda.synchronize()
     return float(np.median(times)) / K, len(times), int(launches), total * 1e-3, (t0, t1)
