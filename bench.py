@@ -44,7 +44,7 @@ H, I = 4096, 14336            # Llama-3-8B MLP (the default workload)
 SIZES = {"hidden": H, "inter": I}
 # DRAM bytes (read + write) of one decode_kernel launch from an ncu capture of this workload,
 # keyed by (hidden, inter, batch); see profiles/
-TRAFFIC = {(4096, 14336, 1): 103057920}
+TRAFFIC = {(4096, 14336, 1): 105265152}
 QT_Q4_K = 3
 EPS = 1e-5
 SEED = 1234

@@ -309,8 +309,9 @@ __device__ __forceinline__ void x_prologue(const Phase& ph, const SmemPlan& plan
     float amax = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    // warp-wide maximum in one instruction: non-negative floats order like their bit patterns
+    // (NaN and Inf sort above every finite value)
+    amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(amax)));
     // x ~ dl * xi with |xi| <= 32000; a non-finite block poisons its outputs with NaN
     float dl = 1.0f, inv = 0.0f;
     if (!(amax <= 3.0e38f)) { dl = __int_as_float(0x7fc00000); }
@@ -333,12 +334,11 @@ __device__ __forceinline__ void x_prologue(const Phase& ph, const SmemPlan& plan
       *reinterpret_cast<uint2*>(xrow) = make_uint2(hi_e, hi_o);
       *reinterpret_cast<uint2*>(xrow + plan.x_stride) = make_uint2(lo_e, lo_o);
     }
-    // sums of xi per 32-element sub-block (4 lanes each)
-    ssum += __shfl_xor_sync(0xffffffffu, ssum, 1);
-    ssum += __shfl_xor_sync(0xffffffffu, ssum, 2);
+    // sums of xi per 32-element sub-block (this lane's eight elements lie in sub-block lane / 4):
+    // one warp-wide integer reduction per sub-block
     int sb[8];
 #pragma unroll
-    for (int j = 0; j < 8; j++) sb[j] = __shfl_sync(0xffffffffu, ssum, 4 * j);
+    for (int j = 0; j < 8; j++) sb[j] = __reduce_add_sync(0xffffffffu, (lane >> 2) == j ? ssum : 0);
     if (lane == 0) delta[m * plan.seg_stride + sg] = dl;
     uint32_t* arow = aux + (size_t)m * plan.aux_stride + sg * AUXW;
     if (lane < 4) {
