@@ -143,6 +143,18 @@ static int run_linear(const void* x, const void* w, const void* bias, void* y, i
     L.w[0] = w; L.rows[0] = N; L.nmat = 1; L.K = K; L.x = x; L.y[0] = y; L.bias[0] = bias;
     return launch_stream_gemv(L, M, dtype, ws->status, st);
   }
+  if (M >= 3 && N > 0 && smallm_supported(qt, M, N, K, dtype, x, w) && !tune_env("MLXR_NO_SMALLM")) {
+    int grid = 0, maxc = 0;
+    size_t part = 0;
+    if (int r = smallm_plan(M, N, K, &grid, &maxc, &part)) return r;
+    Workspace* ws = nullptr;
+    if (int r = get_workspace(st, 0, &ws)) return r;
+    {
+      std::lock_guard<std::mutex> lk(g_ws_mu);
+      if (int r = grow(&ws->part, &ws->part_bytes, part, st)) return r;
+    }
+    return launch_smallm(x, w, bias, y, M, N, K, dtype, ws->status, (float*)ws->part, ws->sync + 16, grid, maxc, st);
+  }
   if (M > 0 && N > 0 && decode_supported(qt, M, K, &w, 1)) {
     Workspace* ws = nullptr;
     if (int r = get_workspace(st, kDecodeScratchBytes, &ws)) return r;

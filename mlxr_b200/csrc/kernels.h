@@ -116,6 +116,13 @@ bool stream_gemv_supported(int qt, int M, int K, const void* const* w, int nmat)
 int launch_stream_gemv(const DecodeLinear& L, int M, int dtype, int* status, cudaStream_t st,
                        const void* next_w = nullptr, size_t next_bytes = 0);
 
+// ---- small-batch tensor-core linear (smallm.cu): Q4_K, 1 <= M <= 64, fp16 / bf16 --------------
+bool smallm_supported(int qt, int M, int N, int K, int dtype, const void* x, const void* w);
+// grid size, the most CTAs that share one output tile, and the bytes of fp32 partial sums needed
+int smallm_plan(int M, int N, int K, int* grid, int* maxc, size_t* partial_bytes);
+int launch_smallm(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int dtype,
+                  int* status, float* partials, uint32_t* counters, int grid, int maxc, cudaStream_t st);
+
 // ---- tensor-core GEMM for batch >= 9 on Q4_K with 16-bit activations (prefill.cu) -------------
 bool prefill_supported(int qt, int M, int N, int K, int dtype, const void* x, const void* w, const void* y);
 int prefill_slices(int M, int N, int K);     // K-slices (grid z); S > 1 needs S*M*N floats of scratch

@@ -5,6 +5,7 @@
 // uses exactly the reference's dequantized weight values (dequant_unit) and accumulates
 // in fp32, the arithmetic of kernel q_gemm_dequant (q_gemm_dequant.metal:443-461).
 #include "common.cuh"
+#include <atomic>
 
 namespace mlxr {
 
@@ -206,12 +207,14 @@ static int launch_gemv_inst(const void* x, const void* w, const void* bias, void
   constexpr int bb = (QT == MLXR_Q4_0) ? 18 : (QT == MLXR_Q4_1) ? 20 : 34;
   constexpr size_t smem = (size_t)MB * kGemvChunk * sizeof(T) + 8 * (size_t)(kGemvChunk / be * bb) + 64;
   auto kern = gemv_rows_kernel<QT, T, MB>;
-  static bool attr_done[64] = {};
+  // set once per device; the call is idempotent, the flags are atomic so that concurrent first
+  // launches from several host threads do not race on them
+  static std::atomic<bool> attr_done[64] = {};
   int dev = 0;
   MLXR_CUDA_TRY(cudaGetDevice(&dev));
-  if (smem > 48 * 1024 && !attr_done[dev & 63]) {
+  if (smem > 48 * 1024 && !attr_done[dev & 63].load(std::memory_order_acquire)) {
     MLXR_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_done[dev & 63] = true;
+    attr_done[dev & 63].store(true, std::memory_order_release);
   }
   kern<<<(N + 7) / 8, 256, smem, st>>>((const T*)x, (const uint8_t*)w, (const T*)bias, (T*)y, M, N, K, row_bytes);
   MLXR_LAUNCH_CHECK("gemv_rows_kernel");
