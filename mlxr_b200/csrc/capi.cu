@@ -153,7 +153,7 @@ static int run_linear(const void* x, const void* w, const void* bias, void* y, i
       std::lock_guard<std::mutex> lk(g_ws_mu);
       if (int r = grow(&ws->part, &ws->part_bytes, part, st)) return r;
     }
-    return launch_smallm(x, w, bias, y, M, N, K, dtype, ws->status, (float*)ws->part, ws->sync + 16, grid, maxc, st);
+    return launch_smallm(x, w, nullptr, bias, y, M, N, K, dtype, ws->status, (float*)ws->part, ws->sync + 16, grid, maxc, st);
   }
   if (M > 0 && N > 0 && decode_supported(qt, M, K, &w, 1)) {
     Workspace* ws = nullptr;
@@ -432,7 +432,13 @@ static int mlp_block_impl(const void* x, const void* norm_weight, const void* w_
   const size_t i_bytes = align_up((size_t)M * inter * es, 256);
   Workspace* ws = nullptr;
   const void* wgu[2] = {w_gate, w_up};
-  const bool decode = decode_supported(qt, M, hidden, wgu, 2) && decode_supported(qt, M, inter, &w_down, 1);
+  // batches 3..64 of Q4_K: RMSNorm, then gate/up with the SiLU(gate) * up epilogue and down on the
+  // small-batch tensor-core kernel (three launches; the decode kernel is built for batch 1-2)
+  const bool small = M >= 3 && smallm_supported(qt, M, inter, hidden, dtype, x, w_gate) &&
+                     smallm_supported(qt, M, inter, hidden, dtype, x, w_up) &&
+                     smallm_supported(qt, M, hidden, inter, dtype, x, w_down) &&
+                     (2 * inter + 127) / 128 <= kSyncWords - 16 && !tune_env("MLXR_NO_SMALLM");
+  const bool decode = !small && decode_supported(qt, M, hidden, wgu, 2) && decode_supported(qt, M, inter, &w_down, 1);
   if (int r = get_workspace(st, decode ? kDecodeScratchBytes : kDecodeScratchBytes + n_bytes + 2 * i_bytes, &ws, 0,
                             decode ? decode_tagged_bytes(M, inter, dtype) : 0))
     return r;
@@ -457,6 +463,21 @@ static int mlp_block_impl(const void* x, const void* norm_weight, const void* w_
   if (norm_weight) {
     if (int r = launch_rmsnorm(x, norm_weight, nullptr, nbuf, M, hidden, eps, dtype, st)) return r;
     n = nbuf;
+  }
+  if (small) {
+    int grid = 0, maxc = 0;
+    size_t part = 0;
+    if (int r = smallm_plan(M, 2 * inter, hidden, &grid, &maxc, &part)) return r;
+    {
+      std::lock_guard<std::mutex> lk(g_ws_mu);
+      if (int r = grow(&ws->part, &ws->part_bytes, part, st)) return r;
+    }
+    if (int r = launch_smallm(n, w_gate, w_up, nullptr, gbuf, M, inter, hidden, dtype, ws->status, (float*)ws->part,
+                              ws->sync + 16, grid, maxc, st))
+      return r;
+    if (!y_f32) return run_linear(gbuf, w_down, nullptr, y, M, hidden, inter, qt, dtype, st);
+    if (int r = run_linear(gbuf, w_down, nullptr, nbuf, M, hidden, inter, qt, dtype, st)) return r;
+    return launch_cast_to_f32(nbuf, (float*)y, (size_t)M * hidden, dtype, st);
   }
   if (int r = run_linear(n, w_gate, nullptr, gbuf, M, inter, hidden, qt, dtype, st)) return r;
   if (int r = run_linear(n, w_up, nullptr, ubuf, M, inter, hidden, qt, dtype, st)) return r;

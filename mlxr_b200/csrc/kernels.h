@@ -118,9 +118,11 @@ int launch_stream_gemv(const DecodeLinear& L, int M, int dtype, int* status, cud
 
 // ---- small-batch tensor-core linear (smallm.cu): Q4_K, 1 <= M <= 64, fp16 / bf16 --------------
 bool smallm_supported(int qt, int M, int N, int K, int dtype, const void* x, const void* w);
-// grid size, the most CTAs that share one output tile, and the bytes of fp32 partial sums needed
-int smallm_plan(int M, int N, int K, int* grid, int* maxc, size_t* partial_bytes);
-int launch_smallm(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int dtype,
+// grid size, the most CTAs that share one output tile, and the bytes of fp32 partial sums needed;
+// rows = weight rows streamed (N, or 2 N for the gate/up form)
+int smallm_plan(int M, int rows, int K, int* grid, int* maxc, size_t* partial_bytes);
+// w2 == nullptr: Y = X W^T (+ bias); otherwise Y = SiLU(X w^T) * (X w2^T) (gate, up; no bias)
+int launch_smallm(const void* x, const void* w, const void* w2, const void* bias, void* y, int M, int N, int K, int dtype,
                   int* status, float* partials, uint32_t* counters, int grid, int maxc, cudaStream_t st);
 
 // ---- tensor-core GEMM for batch >= 9 on Q4_K with 16-bit activations (prefill.cu) -------------

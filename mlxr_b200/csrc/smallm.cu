@@ -72,10 +72,15 @@ struct Params {
 };
 
 struct Shared {
-  uint64_t full_a[kStages];       // the four producer warps of a group have written operand tile s
+  // Operand tile s is used alternately by two k-block groups (k-block 4 i + j sits in stage
+  // (4 i + j) % 6).  Its n-th use signals through barrier pair [s][n & 1], so that each barrier
+  // belongs to one group and every waiter sees consecutive phases of the barrier it polls: with
+  // one barrier per stage, a group running two uses ahead of the other would read the parity of
+  // the use before last as completion.
+  uint64_t full_a[kStages][2];    // the four producer warps of a group have written the tile
   uint64_t x_full[kMaxXStages];   // the four X tiles of a unit have landed
   uint64_t x_empty[kMaxXStages];  // the MMAs that read them are done
-  uint64_t empty[kStages];      // the MMAs that read stage s are done
+  uint64_t empty[kStages][2];     // the MMAs that read it are done
   uint64_t raw_full[kMaxRawStages];
   uint64_t raw_empty[kMaxRawStages];
   uint64_t acc_full[2];         // all MMAs of a tile part are done
@@ -99,6 +104,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr) : "memory");
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// SiLU with the sign-split sigmoid of swiglu_mlp_fused.metal:92-99, on the fast exponential and
+// reciprocal (relative error about 1e-6, far below the rounding to the activation dtype that
+// follows): the epilogue applies it to every batch row in turn, one thread per output column, and
+// the exact expf and division made that serial chain several times longer than the tile's MMAs.
+__device__ __forceinline__ float swish_fast(float x) {
+  const float e = __expf(-fabsf(x));
+  const float s = __fdividef(1.0f, 1.0f + e);      // sigmoid(|x|)
+  return x * (x >= 0.0f ? s : e * s);
 }
 
 __device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -132,9 +147,13 @@ template <int NPAD> struct Rings {
   static constexpr size_t kBytes = (size_t)kStages * kATile + (size_t)kXStages * kXUnit + (size_t)kRawStages * kRawBytes;
 };
 
-template <typename T, int NPAD, int BF>
+// SWIGLU: the tile's rows are 16 gate rows and 16 up rows per TMEM lane quarter (from two weight
+// matrices, wmap and wmap2), Y = SiLU(gate) * up with gate and up rounded to T first, N = the
+// number of gate rows; a tile then covers 64 output columns.
+template <typename T, int NPAD, int BF, bool SWIGLU>
 __global__ void __launch_bounds__(kThreads, 1)
-qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap, const Params P) {
+qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
+                    const __grid_constant__ CUtensorMap wmap2, const Params P) {
   extern __shared__ uint8_t smem_raw[];
 #ifdef MLXR_TUNING
   if (threadIdx.x == 0 && P.trace) {
@@ -146,6 +165,7 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   // the TMA unit fetches a tensor map on first use: ask for both before anything else
   if (threadIdx.x == kWarpRaw * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&wmap)) : "memory");
   if (threadIdx.x == kWarpX * 32) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&xmap)) : "memory");
+  if (SWIGLU && threadIdx.x == kWarpRaw * 32 + 1) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&wmap2)) : "memory");
   using R = Rings<NPAD>;
   constexpr int kXStages = R::kXStages, kRawStages = R::kRawStages, kXTile = R::kXTile, kXUnit = R::kXUnit;
   const uint32_t raw = smem_u32(smem_raw);
@@ -164,10 +184,11 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
   if (tid == 0) {
     sh->dead = 0;
     sh->epi_fail = 0;
-    for (int s = 0; s < kStages; s++) {
-      mbar_init(smem_u32(&sh->full_a[s]), 4);
-      mbar_init(smem_u32(&sh->empty[s]), 1);
-    }
+    for (int s = 0; s < kStages; s++)
+      for (int u = 0; u < 2; u++) {
+        mbar_init(smem_u32(&sh->full_a[s][u]), 4);
+        mbar_init(smem_u32(&sh->empty[s][u]), 1);
+      }
     for (int r = 0; r < kXStages; r++) {
       mbar_init(smem_u32(&sh->x_full[r]), 1);
       mbar_init(smem_u32(&sh->x_empty[r]), 4);       // one commit per k-block group
@@ -216,17 +237,15 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     // convert k-block j of every unit =====
     const int p = tid & (kRows - 1), j = tid >> 7;
     int s = j;                 // stage of k-block 4 i + j
-    uint32_t par = 0;          // parity of that stage's current use
+    int use = 0;               // which use of that stage this is: (4 i + j) / 6
     int r = 0;
     uint32_t rpar = 0;
     for (int i = 0; i < nunits; i++) {
-      if (tid == 0 && i == 6) stamp(25);
 #ifdef MLXR_TUNING
       if (!(P.debug & 2))
 #endif
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->raw_full[r]), rpar, dead))) break;   // warp-uniform
       if (tid == 0 && i == 0) stamp(2);
-      if (tid == 0 && i == 6) stamp(26);
       const uint8_t* rowp = rawring + (size_t)r * kRawBytes + (size_t)p * 144;
       const uint4 ch = *reinterpret_cast<const uint4*>(rowp);
       const uint4 qa = *reinterpret_cast<const uint4*>(rowp + 16 + 32 * j);
@@ -247,9 +266,8 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
       const __half ss0 = __hmul_rn(__int2half_rn(sc_a), d), sm0 = __hmul_rn(__int2half_rn(mn_a), dmin);
       const __half ss1 = __hmul_rn(__int2half_rn(second ? sc_b : sc_a), d), sm1 = __hmul_rn(__int2half_rn(second ? mn_b : mn_a), dmin);
 
-      if (tid == 0 && i == 6) stamp(27);
-      if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->empty[s]), par ^ 1u, dead))) break;     // warp-uniform
-      if (tid == 0 && i == 6) stamp(28);
+      // the MMAs of the stage's previous use (the other group's) must be done
+      if (use > 0 && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->empty[s][(use - 1) & 1]), ((use - 1) >> 1) & 1, dead))) break;   // warp-uniform
       uint8_t* arow = aring + (size_t)s * kATile + (size_t)p * 128;
       const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w}, wb[4] = {qb.x, qb.y, qb.z, qb.w};
       // 16-byte chunk c of row p sits at chunk position c ^ (p & 7) (128-byte swizzle)
@@ -276,12 +294,11 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(arow + (((4 + c) ^ (p & 7)) << 4)) = dequant8_bf16x2(wb[c], s1, m1);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      if (tid == 0 && i == 6) stamp(29);
       __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sh->full_a[s]));
+      if (lane == 0) mbar_arrive(smem_u32(&sh->full_a[s][use & 1]));
       if (tid == 0 && i < 12) stamp(8 + i);
       s += 4;
-      if (s >= kStages) { s -= kStages; par ^= 1u; }
+      if (s >= kStages) { s -= kStages; use++; }
     }
   } else if (warp >= kWarpMma0 && warp < kWarpMma0 + 4) {
     // ===== MMA issuers: warp j (lane 0) multiplies k-block j of every unit into group j's own
@@ -292,18 +309,15 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
       // shared-memory descriptors differ only in their start-address field (bits 0-13, in 16-byte units)
       const uint64_t desc_hi = smem_desc_sw128(0);
       const uint32_t a_lo0 = (smem_u32(aring) & 0x3FFFFu) >> 4, x_lo0 = ((smem_u32(xring) + (uint32_t)j * kXTile) & 0x3FFFFu) >> 4;
-      int s = j, xs = 0, g = 0, sb = sb_first;
-      uint32_t par = 0, xpar = 0;
+      int s = j, use = 0, xs = 0, g = 0, sb = sb_first;
+      uint32_t xpar = 0;
       bool first = true;
       for (int i = 0; i < nunits; i++) {
         const int ab = g & 1;
         bool ok = true;
         if (first) ok = mbar_wait(smem_u32(&sh->acc_empty[ab]), ((g >> 1) & 1) ^ 1u, dead);
-        if (j == 0 && i == 6) stamp(20);
-        ok = ok && mbar_wait(smem_u32(&sh->x_full[xs]), xpar, dead);
-        if (j == 0 && i == 6) stamp(21);
-        ok = ok && mbar_wait(smem_u32(&sh->full_a[s]), par, dead);
-        if (j == 0 && i == 6) stamp(22);
+        ok = ok && mbar_wait(smem_u32(&sh->x_full[xs]), xpar, dead) &&
+             mbar_wait(smem_u32(&sh->full_a[s][use & 1]), (use >> 1) & 1, dead);
         if (!ok) break;
         tc_fence_after();
         const uint32_t dcol = tmem + (uint32_t)((ab * 4 + j) * NPAD);
@@ -315,10 +329,8 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
 #pragma unroll
         for (int k = 0; k < kBK / kUmmaK; k++)
           umma_f16(dcol, adesc + (uint64_t)(k * (kUmmaK * 2 >> 4)), xdesc + (uint64_t)(k * (kUmmaK * 2 >> 4)), idesc, (!first || k > 0) ? 1u : 0u);
-        if (j == 0 && i == 6) stamp(23);
-        umma_commit(smem_u32(&sh->empty[s]));
+        umma_commit(smem_u32(&sh->empty[s][use & 1]));
         umma_commit(smem_u32(&sh->x_empty[xs]));
-        if (j == 0 && i == 6) stamp(30);
         const bool last_of_part = (sb + 1 == P.nsb) || (i + 1 == nunits);
         if (last_of_part) umma_commit(smem_u32(&sh->acc_full[ab]));
         first = false;
@@ -326,26 +338,38 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         if (++sb == P.nsb) sb = 0;
         if (++xs == kXStages) { xs = 0; xpar ^= 1u; }
         s += 4;
-        if (s >= kStages) { s -= kStages; par ^= 1u; }
+        if (s >= kStages) { s -= kStages; use++; }
       }
     }
   } else if (warp == kWarpRaw) {
-    // ===== packed weights: one box of 128 rows x 144 bytes per unit =====
-    if (lane == 0) {
+    // ===== packed weights: one box of 128 rows x 144 bytes per unit; for gate/up eight boxes of
+    // 16 rows, issued by eight lanes at once (one thread issuing eight copies per unit was the
+    // kernel's pace).  The whole warp walks the loop. =====
+    {
       int issued = 0, t = t_first, sb = sb_first;
       for (int i = 0; i < nunits; i++) {
         const int r = i % kRawStages, rit = i / kRawStages;
 #ifdef MLXR_TUNING
         if (P.debug & 2) { issued = 0; continue; }
 #endif
-        if (!mbar_wait(smem_u32(&sh->raw_empty[r]), (rit & 1) ^ 1, dead)) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->raw_empty[r]), (rit & 1) ^ 1, dead))) break;
         const uint32_t bar = smem_u32(&sh->raw_full[r]);
-        mbar_expect_tx(bar, kRawBytes);
-        tma_load_2d(smem_u32(rawring + (size_t)r * kRawBytes), &wmap, 18 * sb, t * kRows, bar);
+        if (lane == 0) mbar_expect_tx(bar, kRawBytes);
+        __syncwarp();
+        if constexpr (SWIGLU) {
+          // lane q < 4: gate rows 64 t + 16 q .. + 15 -> tile rows 32 q ..; lane 4 + q: the same rows of up -> 32 q + 16 ..
+          const int q = lane & 3;
+          const uint32_t dst = smem_u32(rawring + (size_t)r * kRawBytes + (size_t)(32 * q + (lane < 4 ? 0 : 16)) * 144);
+          if (lane < 4) tma_load_2d(dst, &wmap, 18 * sb, 64 * t + 16 * q, bar);
+          else if (lane < 8) tma_load_2d(dst, &wmap2, 18 * sb, 64 * t + 16 * q, bar);
+        } else {
+          if (lane == 0) tma_load_2d(smem_u32(rawring + (size_t)r * kRawBytes), &wmap, 18 * sb, t * kRows, bar);
+        }
+        __syncwarp();
         issued = i + 1;
         if (++sb == P.nsb) { sb = 0; t++; }
       }
-      if (*dead) {   // copies in flight must land before the CTA may exit (bounded)
+      if (*dead && lane == 0) {   // copies in flight must land before the CTA may exit (bounded)
         for (int i = max(0, issued - kRawStages); i < issued; i++) {
           const uint32_t bar = smem_u32(&sh->raw_full[i % kRawStages]);
           for (uint32_t sp = 0; sp < kSpin; sp++) if (mbar_try(bar, (i / kRawStages) & 1)) break;
@@ -393,10 +417,22 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
       tc_fence_after();
       if (et == 0) stamp(g == 0 ? 6 : 24);
       const bool whole = cnt == P.nsb;       // this CTA summed the tile's whole K: store Y directly
-      const int n = t * kRows + rt;
+      // output column of this lane: its weight row, or for SWIGLU the gate row that lanes l and l + 16 share
+      const int n = SWIGLU ? 64 * t + 16 * quarter + (lane & 15) : t * kRows + rt;
+      const bool writer = (!SWIGLU || lane < 16) && n < P.N;
+      // sums of one batch row -> Y: plain (+ bias), or SiLU(gate) * up across the lane pair
+      auto finish = [&](float v, float bv) -> T {
+        if constexpr (SWIGLU) {
+          const float o = __shfl_xor_sync(0xffffffffu, v, 16);        // lanes < 16: v = gate, o = up
+          const float gv = Act<T>::to_f(Act<T>::from_f(v)), uv = Act<T>::to_f(Act<T>::from_f(o));
+          return Act<T>::from_f(swish_fast(gv) * uv);
+        } else {
+          return Act<T>::from_f(v + bv);
+        }
+      };
       const int slot = whole ? 0 : cta - unit_owner(P.U, G, (long long)t * P.nsb);
       float* part = P.partials + (((size_t)t * P.maxc + slot) * NPAD) * kRows + rt;
-      const float bv = (whole && bias && n < P.N) ? Act<T>::to_f(bias[n]) : 0.0f;
+      const float bv = (!SWIGLU && bias && n < P.N) ? Act<T>::to_f(bias[n]) : 0.0f;
 #pragma unroll 1
       for (int c0 = 0; c0 < NPAD; c0 += 16) {
         // the four groups' sums of these 16 batch columns, added in group order
@@ -410,10 +446,12 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
           for (int c = 0; c < 16; c++) r[c] = __float_as_uint(__uint_as_float(r[c]) + __uint_as_float(q[c]));
         }
         if (whole) {
-          if (n < P.N) {
 #pragma unroll
-            for (int c = 0; c < 16; c++)
-              if (c0 + c < P.M) reinterpret_cast<T*>(P.y)[(size_t)(c0 + c) * P.N + n] = Act<T>::from_f(__uint_as_float(r[c]) + bv);
+          for (int c = 0; c < 16; c++) {
+            if (c0 + c < P.M) {             // uniform: every lane takes part in the exchange
+              const T o = finish(__uint_as_float(r[c]), bv);
+              if (writer) reinterpret_cast<T*>(P.y)[(size_t)(c0 + c) * P.N + n] = o;
+            }
           }
         } else {
 #pragma unroll
@@ -438,22 +476,31 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         }
         epi_barrier();
         const int nc = *reinterpret_cast<volatile int*>(&sh->last);
-        if (nc && n < P.N) {
+        if (nc) {
           const float* src = P.partials + ((size_t)t * P.maxc * NPAD) * kRows + rt;
-          const float bl = bias ? Act<T>::to_f(bias[n]) : 0.0f;
-          // eight batch rows at a time: all of their loads are in flight before the first store
-          for (int m0 = 0; m0 < P.M; m0 += 8) {
-            float v[8];
+          // sixteen batch rows and two parts at a time: 32 loads in flight per thread (one load
+          // after the other, each L2 round trip would be paid M * nc times)
+          for (int m0 = 0; m0 < P.M; m0 += 16) {
+            float v[16];
 #pragma unroll
-            for (int e = 0; e < 8; e++) v[e] = 0.0f;
-            for (int z = 0; z < nc; z++) {
+            for (int e = 0; e < 16; e++) v[e] = 0.0f;
+            for (int z = 0; z < nc; z += 2) {
+              float a[16], b[16];
+              const bool two = z + 1 < nc;
 #pragma unroll
-              for (int e = 0; e < 8; e++)
-                if (m0 + e < P.M) v[e] += __ldcg(src + ((size_t)z * NPAD + m0 + e) * kRows);
+              for (int e = 0; e < 16; e++) a[e] = (m0 + e < P.M) ? __ldcg(src + ((size_t)z * NPAD + m0 + e) * kRows) : 0.0f;
+#pragma unroll
+              for (int e = 0; e < 16; e++) b[e] = (two && m0 + e < P.M) ? __ldcg(src + ((size_t)(z + 1) * NPAD + m0 + e) * kRows) : 0.0f;
+#pragma unroll
+              for (int e = 0; e < 16; e++) { v[e] += a[e]; v[e] += b[e]; }
             }
 #pragma unroll
-            for (int e = 0; e < 8; e++)
-              if (m0 + e < P.M) reinterpret_cast<T*>(P.y)[(size_t)(m0 + e) * P.N + n] = Act<T>::from_f(v[e] + bl);
+            for (int e = 0; e < 16; e++) {
+              if (m0 + e < P.M) {
+                const T o = finish(v[e], bv);
+                if (writer) reinterpret_cast<T*>(P.y)[(size_t)(m0 + e) * P.N + n] = o;
+              }
+            }
           }
         }
       }
@@ -518,7 +565,8 @@ bool smallm_supported(int qt, int M, int N, int K, int dtype, const void* x, con
   return true;
 }
 
-int smallm_plan(int M, int N, int K, int* grid, int* maxc, size_t* partial_bytes) {
+int smallm_plan(int M, int rows, int K, int* grid, int* maxc, size_t* partial_bytes) {
+  const int N = rows;
   int sms = 0;
   if (int r = device_sms(&sms)) return r;
   const int nsb = K / 256, ntiles = (N + smallm::kRows - 1) / smallm::kRows;
@@ -533,10 +581,11 @@ int smallm_plan(int M, int N, int K, int* grid, int* maxc, size_t* partial_bytes
   return MLXR_OK;
 }
 
-template <typename T, int NPAD, int BF>
-static int launch_inst(const CUtensorMap& xmap, const CUtensorMap& wmap, const smallm::Params& P, int grid, cudaStream_t st) {
+template <typename T, int NPAD, int BF, bool SWIGLU>
+static int launch_inst(const CUtensorMap& xmap, const CUtensorMap& wmap, const CUtensorMap& wmap2, const smallm::Params& P, int grid,
+                       cudaStream_t st) {
   using namespace smallm;
-  auto kern = qgemm_smallm_kernel<T, NPAD, BF>;
+  auto kern = qgemm_smallm_kernel<T, NPAD, BF, SWIGLU>;
   constexpr size_t smem = Rings<NPAD>::kBytes + sizeof(Shared) + 1024;
   static std::atomic<bool> attr_done[64] = {};
   int dev = 0;
@@ -555,17 +604,34 @@ static int launch_inst(const CUtensorMap& xmap, const CUtensorMap& wmap, const s
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
   cfg.numAttrs = 1;
-  MLXR_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, xmap, wmap, P));
+  MLXR_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, xmap, wmap, wmap2, P));
   count_launch();
   return MLXR_OK;
 }
 
-int launch_smallm(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int dtype,
+// Packed rows as 8-byte elements, boxes of one super-block (18 elements) x `box_rows` rows; rows past N read as zero.
+static int weight_map(EncodeTiledFn encode, const void* w, int N, int K, int box_rows, CUtensorMap* out) {
+  const size_t row_bytes = (size_t)(K / 256) * 144;
+  const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 8), (cuuint64_t)N};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {18, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(w), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%d) for W [%d rows of %zu bytes]", (int)r, N, row_bytes); return MLXR_ERR_CUDA; }
+  return MLXR_OK;
+}
+
+// w2 == nullptr: Y[M, N] = X W^T (+ bias).  Otherwise w = gate, w2 = up (both [N, K]) and
+// Y[M, N] = SiLU(X gate^T) * (X up^T), the two products rounded to the activation dtype first.
+int launch_smallm(const void* x, const void* w, const void* w2, const void* bias, void* y, int M, int N, int K, int dtype,
                   int* status, float* partials, uint32_t* counters, int grid, int maxc, cudaStream_t st) {
   EncodeTiledFn encode = nullptr;
   if (int r = tensor_map_encoder(&encode)) return r;
   const int npad = smallm_npad(M);
-  CUtensorMap xmap, wmap;
+  const bool swiglu = w2 != nullptr;
+  CUtensorMap xmap, wmap, wmap2;
   {
     // X [M, K] of a 16-bit type (K inner), boxes of 64 x NPAD with the 128-byte swizzle; rows past M read as zero
     const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
@@ -577,25 +643,15 @@ int launch_smallm(const void* x, const void* w, const void* bias, void* y, int M
                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%d) for X [%d, %d]", (int)r, M, K); return MLXR_ERR_CUDA; }
   }
-  {
-    // packed rows as 8-byte elements, boxes of one super-block (18 elements) x 128 rows; rows past N read as zero
-    const size_t row_bytes = (size_t)(K / 256) * 144;
-    const cuuint64_t dims[2] = {(cuuint64_t)(row_bytes / 8), (cuuint64_t)N};
-    const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
-    const cuuint32_t box[2] = {18, (cuuint32_t)smallm::kRows};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = encode(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<void*>(w), dims, strides, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%d) for W [%d rows of %zu bytes]", (int)r, N, row_bytes); return MLXR_ERR_CUDA; }
-  }
+  if (int r = weight_map(encode, w, N, K, swiglu ? 16 : smallm::kRows, &wmap)) return r;
+  if (int r = weight_map(encode, swiglu ? w2 : w, N, K, swiglu ? 16 : smallm::kRows, &wmap2)) return r;
   smallm::Params P;
   memset(&P, 0, sizeof(P));
   P.bias = bias;
   P.y = y;
   P.M = M; P.N = N; P.K = K;
   P.nsb = K / 256;
-  P.ntiles = (N + smallm::kRows - 1) / smallm::kRows;
+  P.ntiles = ((swiglu ? 2 * N : N) + smallm::kRows - 1) / smallm::kRows;
   P.maxc = maxc;
   P.U = (long long)P.ntiles * P.nsb;
   P.status = status;
@@ -604,16 +660,17 @@ int launch_smallm(const void* x, const void* w, const void* bias, void* y, int M
   if (const char* e = tune_env("MLXR_SM_DEBUG")) P.debug = atoi(e);   // tuning probe
 #ifdef MLXR_TUNING
   P.trace = (unsigned long long*)get_decode_trace();
+  if (P.trace && swiglu) P.trace += 256 * 32;
 #endif
   int rc = MLXR_ERR_UNSUPPORTED;
-#define MLXR_SMALLM_BY_NPAD(T, BF)                                                       \
+#define MLXR_SMALLM_BY_NPAD(T, BF, SW)                                                    \
   do {                                                                                    \
-    if (npad == 16) rc = launch_inst<T, 16, BF>(xmap, wmap, P, grid, st);                 \
-    else if (npad == 32) rc = launch_inst<T, 32, BF>(xmap, wmap, P, grid, st);            \
-    else rc = launch_inst<T, 64, BF>(xmap, wmap, P, grid, st);                            \
+    if (npad == 16) rc = launch_inst<T, 16, BF, SW>(xmap, wmap, wmap2, P, grid, st);      \
+    else if (npad == 32) rc = launch_inst<T, 32, BF, SW>(xmap, wmap, wmap2, P, grid, st); \
+    else rc = launch_inst<T, 64, BF, SW>(xmap, wmap, wmap2, P, grid, st);                 \
   } while (0)
-  if (dtype == MLXR_F16) MLXR_SMALLM_BY_NPAD(__half, 0);
-  else MLXR_SMALLM_BY_NPAD(__nv_bfloat16, 1);
+  if (dtype == MLXR_F16) { if (swiglu) MLXR_SMALLM_BY_NPAD(__half, 0, true); else MLXR_SMALLM_BY_NPAD(__half, 0, false); }
+  else { if (swiglu) MLXR_SMALLM_BY_NPAD(__nv_bfloat16, 1, true); else MLXR_SMALLM_BY_NPAD(__nv_bfloat16, 1, false); }
 #undef MLXR_SMALLM_BY_NPAD
   return rc;
 }
