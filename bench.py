@@ -287,8 +287,10 @@ def random_packed(N, K, qt, device, seed):
 def secondary_measurements(world, rank, local, ctx, args, dist):
     """The other parts of the benchmark definition, each as its own small measurement with its own
     roofline: prefill Q-GEMM (TFLOP/s against the measured bf16 peak), the M = 1 GEMV per format
-    (GB/s against the measured HBM peak), the TinyLlama-shaped block, and the Llama-3-70B-shaped
-    block at batch 1 and 32 on this number of GPUs.  Single-GPU entries run on rank 0 only."""
+    (GB/s against the measured HBM peak), the TinyLlama-shaped block, the small-batch range (one
+    linear at batch 8 / 16 / 32 / 64, the Llama-3-8B-shaped block at batch 8 and 32), and the
+    Llama-3-70B-shaped block at batch 1 and 32 on this number of GPUs.  Single-GPU entries run on
+    rank 0 only."""
     import torch
     from mlxr_b200._capi import check, lib
     hbm, tf, which = measured_peaks()
@@ -373,6 +375,12 @@ def secondary_measurements(world, rank, local, ctx, args, dist):
         for fmt in ("q4_k", "q4_0", "q8_0", "nf4"):
             out.append(linear_entry(fmt, 1, 14336, 4096, 0.03))
         out.append(block_entry("TinyLlama-shaped Q4_0 decode MLP block, batch 1, fp16", 2048, 5632, 0, 1, 0, torch.float16, 0.03, False))
+        # the small-batch range (batch 8 / 32 / 64 of the decode configuration): one linear and the block
+        for M in (8, 16, 32, 64):
+            out.append(linear_entry("q4_k", M, 14336, 4096, 0.03))
+        for M in (8, 32):
+            out.append(block_entry(f"Llama-3-8B-shaped Q4_K decode MLP block, batch {M}, bf16", 4096, 14336, QT_Q4_K, M, 1,
+                                   torch.bfloat16, 0.03, False))
     # the 70B-shaped block on this number of GPUs (every rank takes part)
     for M in (1, 32):
         e = block_entry(f"Llama-3-70B-shaped Q4_K decode MLP block, batch {M}, bf16, {world} GPU(s)", 8192, 28672, QT_Q4_K, M, 1,
