@@ -299,6 +299,15 @@ MLXR_API int mlxr_set_decode_launch_mode(int mode);
  * landed, [3] first tile accumulated (phase 0; +4 for phase 1), [15]/[14] end. */
 MLXR_API int mlxr_debug_set_trace_buffer(void* dev_ptr);
 
+/* Work partition of the small-batch tensor-core linear (no counterpart in the reference; host
+ * arithmetic only, usable without a GPU): `units` work units (tile of 128 weight rows x 256-wide
+ * super-block of K, tile-major) are dealt to `ctas` CTAs in contiguous ranges.  Writes the first
+ * unit of CTA `cta` and of CTA `cta + 1` to begin / end, and the CTA that owns `unit` to owner
+ * (each may be NULL).  MLXR_ERR_INVALID_ARGUMENT unless 1 <= ctas <= units, 0 <= cta < ctas,
+ * 0 <= unit < units. */
+MLXR_API int mlxr_debug_smallm_partition(long long units, int ctas, int cta, long long unit,
+                                         long long* begin, long long* end, int* owner);
+
 /* Attention input projections with RoPE on q and k: n = rmsnorm(x) (norm_weight may be
  * NULL), q = n Wq^T, k = n Wk^T, v = n Wv^T, then rope_apply on q and k
  * (Attention::forward, core/graph/layers.cpp:266-278, with the rope_apply primitive).

@@ -51,6 +51,7 @@ PROTOTYPES = {
     "mlxr_set_wait_limit_ns": (_i, [C.c_uint64]),
     "mlxr_static_status": (_i, [_vp, _vp]),
     "mlxr_debug_set_trace_buffer": (_i, [_vp]),
+    "mlxr_debug_smallm_partition": (_i, [C.c_longlong, _i, _i, C.c_longlong, _vp, _vp, _vp]),
     "mlxr_set_decode_launch_mode": (_i, [_i]),
     "mlxr_q_gemm_dequant_static": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "mlxr_qkv_rope": (_i, [_vp] * 11 + [_i] * 7 + [_f, _i, _i, _vp]),

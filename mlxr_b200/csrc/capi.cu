@@ -153,7 +153,7 @@ static int run_linear(const void* x, const void* w, const void* bias, void* y, i
       std::lock_guard<std::mutex> lk(g_ws_mu);
       if (int r = grow(&ws->part, &ws->part_bytes, part, st)) return r;
     }
-    return launch_smallm(x, w, nullptr, bias, y, M, N, K, dtype, ws->status, (float*)ws->part, ws->sync + 16, grid, maxc, st);
+    return launch_smallm(x, w, nullptr, bias, y, M, N, K, qt, dtype, ws->status, (float*)ws->part, ws->sync + 16, grid, maxc, st);
   }
   if (M > 0 && N > 0 && decode_supported(qt, M, K, &w, 1)) {
     Workspace* ws = nullptr;
@@ -472,7 +472,7 @@ static int mlp_block_impl(const void* x, const void* norm_weight, const void* w_
       std::lock_guard<std::mutex> lk(g_ws_mu);
       if (int r = grow(&ws->part, &ws->part_bytes, part, st)) return r;
     }
-    if (int r = launch_smallm(n, w_gate, w_up, nullptr, gbuf, M, inter, hidden, dtype, ws->status, (float*)ws->part,
+    if (int r = launch_smallm(n, w_gate, w_up, nullptr, gbuf, M, inter, hidden, qt, dtype, ws->status, (float*)ws->part,
                               ws->sync + 16, grid, maxc, st))
       return r;
     if (!y_f32) return run_linear(gbuf, w_down, nullptr, y, M, hidden, inter, qt, dtype, st);
@@ -532,6 +532,15 @@ int mlxr_set_decode_launch_mode(int mode) {
 int mlxr_set_wait_limit_ns(uint64_t ns) {
   if (ns == 0) { set_error("mlxr_set_wait_limit_ns: the limit must be positive"); return MLXR_ERR_INVALID_ARGUMENT; }
   set_wait_limit_ns(ns);
+  return MLXR_OK;
+}
+
+int mlxr_debug_smallm_partition(long long units, int ctas, int cta, long long unit, long long* begin, long long* end, int* owner) {
+  if (units < 1 || ctas < 1 || ctas > units || cta < 0 || cta >= ctas || unit < 0 || unit >= units) {
+    set_error("partition: need 1 <= ctas <= units, 0 <= cta < ctas, 0 <= unit < units");
+    return MLXR_ERR_INVALID_ARGUMENT;
+  }
+  smallm_partition(units, ctas, cta, unit, begin, end, owner);
   return MLXR_OK;
 }
 

@@ -116,13 +116,14 @@ bool stream_gemv_supported(int qt, int M, int K, const void* const* w, int nmat)
 int launch_stream_gemv(const DecodeLinear& L, int M, int dtype, int* status, cudaStream_t st,
                        const void* next_w = nullptr, size_t next_bytes = 0);
 
-// ---- small-batch tensor-core linear (smallm.cu): Q4_K, 1 <= M <= 64, fp16 / bf16 --------------
+// ---- small-batch tensor-core linear (smallm.cu): Q4_K / Q4_0, 1 <= M <= 64, fp16 / bf16 --------------
 bool smallm_supported(int qt, int M, int N, int K, int dtype, const void* x, const void* w);
+void smallm_partition(long long units, int ctas, int cta, long long unit, long long* begin, long long* end, int* owner);
 // grid size, the most CTAs that share one output tile, and the bytes of fp32 partial sums needed;
 // rows = weight rows streamed (N, or 2 N for the gate/up form)
 int smallm_plan(int M, int rows, int K, int* grid, int* maxc, size_t* partial_bytes);
 // w2 == nullptr: Y = X W^T (+ bias); otherwise Y = SiLU(X w^T) * (X w2^T) (gate, up; no bias)
-int launch_smallm(const void* x, const void* w, const void* w2, const void* bias, void* y, int M, int N, int K, int dtype,
+int launch_smallm(const void* x, const void* w, const void* w2, const void* bias, void* y, int M, int N, int K, int qt, int dtype,
                   int* status, float* partials, uint32_t* counters, int grid, int maxc, cudaStream_t st);
 
 // ---- tensor-core GEMM for batch >= 9 on Q4_K with 16-bit activations (prefill.cu) -------------

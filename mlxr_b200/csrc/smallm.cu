@@ -1,7 +1,9 @@
-// Small-batch Q4_K linear (3 <= M <= 64 rows of X) on the 5th-generation tensor cores.
+// Small-batch Q4_K / Q4_0 linear (3 <= M <= 64 rows of X) on the 5th-generation tensor cores.
 //
-//   Y[M, N] = X[M, K] * dequant(W)[N, K]^T (+ bias),  X, Y fp16 or bf16, W in MLXR's Q4_K layout
-//   (q_gemm_dequant.metal:205-260; q_gemm_dequant_primitive.mm:186-203 for the host contract)
+//   Y[M, N] = X[M, K] * dequant(W)[N, K]^T (+ bias),  X, Y fp16 or bf16, W in MLXR's Q4_K or Q4_0
+//   layout (q_gemm_dequant.metal:205-260 and 142-161; q_gemm_dequant_primitive.mm:186-203 for the
+//   host contract).  Both formats spend 144 bytes per 256 weights of a row, so the staging is the
+//   same and only the producers' reading of the bytes differs.
 //
 // At these batch sizes the linear is bound by the stream of packed weights from HBM, and the
 // work per byte is the conversion of the weights, not the product.  The roles of the operands
@@ -150,7 +152,7 @@ template <int NPAD> struct Rings {
 // SWIGLU: the tile's rows are 16 gate rows and 16 up rows per TMEM lane quarter (from two weight
 // matrices, wmap and wmap2), Y = SiLU(gate) * up with gate and up rounded to T first, N = the
 // number of gate rows; a tile then covers 64 output columns.
-template <typename T, int NPAD, int BF, bool SWIGLU>
+template <int QT, typename T, int NPAD, int BF, bool SWIGLU>
 __global__ void __launch_bounds__(kThreads, 1)
 qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant__ CUtensorMap wmap,
                     const __grid_constant__ CUtensorMap wmap2, const Params P) {
@@ -247,36 +249,56 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
       if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->raw_full[r]), rpar, dead))) break;   // warp-uniform
       if (tid == 0 && i == 0) stamp(2);
       const uint8_t* rowp = rawring + (size_t)r * kRawBytes + (size_t)p * 144;
-      const uint4 ch = *reinterpret_cast<const uint4*>(rowp);
-      const uint4 qa = *reinterpret_cast<const uint4*>(rowp + 16 + 32 * j);
-      const uint4 qb = *reinterpret_cast<const uint4*>(rowp + 32 + 32 * j);
+      // this thread's 64 weights (two sub-blocks) as eight words of nibbles, element order = nibble
+      // order in both formats, and each sub-block's scale and min in fp16
+      uint32_t wa[4], wb[4];
+      __half ss0, sm0, ss1, sm1;
+      if constexpr (QT == MLXR_Q4_K) {
+        const uint4 ch = *reinterpret_cast<const uint4*>(rowp);
+        const uint4 qa = *reinterpret_cast<const uint4*>(rowp + 16 + 32 * j);
+        const uint4 qb = *reinterpret_cast<const uint4*>(rowp + 32 + 32 * j);
+        wa[0] = qa.x; wa[1] = qa.y; wa[2] = qa.z; wa[3] = qa.w;
+        wb[0] = qb.x; wb[1] = qb.y; wb[2] = qb.z; wb[3] = qb.w;
+        // header: d, dmin (fp16), scales[12]; group j >> 1 reads scales[3 (j >> 1) ..] as one 24-bit
+        // value.  Sub-block 2 j + hb has offset (2 j + hb) & 3 in its group: offset 1 takes the
+        // second (scale, min) pair, offsets 0, 2 and 3 the first (q_gemm_dequant.metal:222-242)
+        const __half d = __ushort_as_half((unsigned short)(ch.x & 0xFFFFu));
+        const __half dmin = __ushort_as_half((unsigned short)(ch.x >> 16));
+        const uint32_t t24 = (j & 2) ? ((ch.y >> 24) | ((ch.z & 0xFFFFu) << 8)) : (ch.y & 0xFFFFFFu);
+        const uint32_t b0 = t24 & 0xFFu, b1 = (t24 >> 8) & 0xFFu, b2 = (t24 >> 16) & 0xFFu;
+        const int sc_a = (int)(b0 & 0x3Fu), mn_a = (int)(((b0 >> 6) | ((b1 & 0x0Fu) << 2)) & 0x3Fu);
+        const int sc_b = (int)(((b1 >> 4) | ((b2 & 0x03u) << 4)) & 0x3Fu), mn_b = (int)((b2 >> 2) & 0x3Fu);
+        const bool second = (j & 1) == 0;      // sub-block 2 j + 1 has offset 1 only for even j
+        ss0 = __hmul_rn(__int2half_rn(sc_a), d); sm0 = __hmul_rn(__int2half_rn(mn_a), dmin);
+        ss1 = __hmul_rn(__int2half_rn(second ? sc_b : sc_a), d); sm1 = __hmul_rn(__int2half_rn(second ? mn_b : mn_a), dmin);
+      } else {
+        // Q4_0 (q_gemm_dequant.metal:142-161): eight 18-byte blocks {fp16 d, 16 bytes of nibbles} fill
+        // the same 144 bytes per 256 weights.  Blocks 2 j and 2 j + 1 are the 36 bytes from 36 j:
+        // d0 | 16 nibble bytes (2 bytes off a word boundary) | d1 | 16 nibble bytes (aligned)
+        const uint32_t* wp = reinterpret_cast<const uint32_t*>(rowp + 36 * j);
+        uint32_t W[9];
+#pragma unroll
+        for (int q = 0; q < 9; q++) W[q] = wp[q];
+#pragma unroll
+        for (int q = 0; q < 4; q++) { wa[q] = __funnelshift_r(W[q], W[q + 1], 16); wb[q] = W[5 + q]; }
+        ss0 = __ushort_as_half((unsigned short)(W[0] & 0xFFFFu));
+        ss1 = __ushort_as_half((unsigned short)(W[4] >> 16));
+        sm0 = sm1 = __ushort_as_half((unsigned short)0);
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sh->raw_empty[r]));
       if (++r == kRawStages) { r = 0; rpar ^= 1u; }
-      // header: d, dmin (fp16), scales[12]; group j >> 1 reads scales[3 (j >> 1) ..] as one 24-bit
-      // value.  Sub-block 2 j + hb has offset (2 j + hb) & 3 in its group: offset 1 takes the
-      // second (scale, min) pair, offsets 0, 2 and 3 the first (q_gemm_dequant.metal:222-242)
-      const __half d = __ushort_as_half((unsigned short)(ch.x & 0xFFFFu));
-      const __half dmin = __ushort_as_half((unsigned short)(ch.x >> 16));
-      const uint32_t t24 = (j & 2) ? ((ch.y >> 24) | ((ch.z & 0xFFFFu) << 8)) : (ch.y & 0xFFFFFFu);
-      const uint32_t b0 = t24 & 0xFFu, b1 = (t24 >> 8) & 0xFFu, b2 = (t24 >> 16) & 0xFFu;
-      const int sc_a = (int)(b0 & 0x3Fu), mn_a = (int)(((b0 >> 6) | ((b1 & 0x0Fu) << 2)) & 0x3Fu);
-      const int sc_b = (int)(((b1 >> 4) | ((b2 & 0x03u) << 4)) & 0x3Fu), mn_b = (int)((b2 >> 2) & 0x3Fu);
-      const bool second = (j & 1) == 0;      // sub-block 2 j + 1 has offset 1 only for even j
-      const __half ss0 = __hmul_rn(__int2half_rn(sc_a), d), sm0 = __hmul_rn(__int2half_rn(mn_a), dmin);
-      const __half ss1 = __hmul_rn(__int2half_rn(second ? sc_b : sc_a), d), sm1 = __hmul_rn(__int2half_rn(second ? mn_b : mn_a), dmin);
 
       // the MMAs of the stage's previous use (the other group's) must be done
       if (use > 0 && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->empty[s][(use - 1) & 1]), ((use - 1) >> 1) & 1, dead))) break;   // warp-uniform
       uint8_t* arow = aring + (size_t)s * kATile + (size_t)p * 128;
-      const uint32_t wa[4] = {qa.x, qa.y, qa.z, qa.w}, wb[4] = {qb.x, qb.y, qb.z, qb.w};
       // 16-byte chunk c of row p sits at chunk position c ^ (p & 7) (128-byte swizzle)
 #ifdef MLXR_TUNING
       if (P.debug & 1) {
 #pragma unroll
-        for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(arow + ((c ^ (p & 7)) << 4)) = qa;
+        for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(arow + ((c ^ (p & 7)) << 4)) = make_uint4(wa[0], wa[1], wa[2], wa[3]);
 #pragma unroll
-        for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(arow + (((4 + c) ^ (p & 7)) << 4)) = qb;
+        for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(arow + (((4 + c) ^ (p & 7)) << 4)) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
       } else
 #endif
       if constexpr (BF == 0) {
@@ -557,8 +579,14 @@ static int device_sms(int* out) {
 
 static int smallm_npad(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : 64; }
 
+void smallm_partition(long long units, int ctas, int cta, long long unit, long long* begin, long long* end, int* owner) {
+  if (begin) *begin = smallm::unit_begin(units, ctas, cta);
+  if (end) *end = smallm::unit_begin(units, ctas, cta + 1);
+  if (owner) *owner = smallm::unit_owner(units, ctas, unit);
+}
+
 bool smallm_supported(int qt, int M, int N, int K, int dtype, const void* x, const void* w) {
-  if (qt != MLXR_Q4_K || (dtype != MLXR_F16 && dtype != MLXR_BF16)) return false;
+  if ((qt != MLXR_Q4_K && qt != MLXR_Q4_0) || (dtype != MLXR_F16 && dtype != MLXR_BF16)) return false;
   if (M < 1 || M > 64 || N < 1 || K < 256 || K % 256 != 0) return false;
   if ((((uintptr_t)x) | ((uintptr_t)w)) & 15u) return false;
   if ((N + smallm::kRows - 1) / smallm::kRows > kSyncWords - 16) return false;   // one counter per tile
@@ -581,11 +609,11 @@ int smallm_plan(int M, int rows, int K, int* grid, int* maxc, size_t* partial_by
   return MLXR_OK;
 }
 
-template <typename T, int NPAD, int BF, bool SWIGLU>
+template <int QT, typename T, int NPAD, int BF, bool SWIGLU>
 static int launch_inst(const CUtensorMap& xmap, const CUtensorMap& wmap, const CUtensorMap& wmap2, const smallm::Params& P, int grid,
                        cudaStream_t st) {
   using namespace smallm;
-  auto kern = qgemm_smallm_kernel<T, NPAD, BF, SWIGLU>;
+  auto kern = qgemm_smallm_kernel<QT, T, NPAD, BF, SWIGLU>;
   constexpr size_t smem = Rings<NPAD>::kBytes + sizeof(Shared) + 1024;
   static std::atomic<bool> attr_done[64] = {};
   int dev = 0;
@@ -625,7 +653,7 @@ static int weight_map(EncodeTiledFn encode, const void* w, int N, int K, int box
 
 // w2 == nullptr: Y[M, N] = X W^T (+ bias).  Otherwise w = gate, w2 = up (both [N, K]) and
 // Y[M, N] = SiLU(X gate^T) * (X up^T), the two products rounded to the activation dtype first.
-int launch_smallm(const void* x, const void* w, const void* w2, const void* bias, void* y, int M, int N, int K, int dtype,
+int launch_smallm(const void* x, const void* w, const void* w2, const void* bias, void* y, int M, int N, int K, int qt, int dtype,
                   int* status, float* partials, uint32_t* counters, int grid, int maxc, cudaStream_t st) {
   EncodeTiledFn encode = nullptr;
   if (int r = tensor_map_encoder(&encode)) return r;
@@ -663,14 +691,21 @@ int launch_smallm(const void* x, const void* w, const void* w2, const void* bias
   if (P.trace && swiglu) P.trace += 256 * 32;
 #endif
   int rc = MLXR_ERR_UNSUPPORTED;
-#define MLXR_SMALLM_BY_NPAD(T, BF, SW)                                                    \
-  do {                                                                                    \
-    if (npad == 16) rc = launch_inst<T, 16, BF, SW>(xmap, wmap, wmap2, P, grid, st);      \
-    else if (npad == 32) rc = launch_inst<T, 32, BF, SW>(xmap, wmap, wmap2, P, grid, st); \
-    else rc = launch_inst<T, 64, BF, SW>(xmap, wmap, wmap2, P, grid, st);                 \
+#define MLXR_SMALLM_BY_NPAD(QTV, T, BF, SW)                                                    \
+  do {                                                                                         \
+    if (npad == 16) rc = launch_inst<QTV, T, 16, BF, SW>(xmap, wmap, wmap2, P, grid, st);      \
+    else if (npad == 32) rc = launch_inst<QTV, T, 32, BF, SW>(xmap, wmap, wmap2, P, grid, st); \
+    else rc = launch_inst<QTV, T, 64, BF, SW>(xmap, wmap, wmap2, P, grid, st);                 \
   } while (0)
-  if (dtype == MLXR_F16) { if (swiglu) MLXR_SMALLM_BY_NPAD(__half, 0, true); else MLXR_SMALLM_BY_NPAD(__half, 0, false); }
-  else { if (swiglu) MLXR_SMALLM_BY_NPAD(__nv_bfloat16, 1, true); else MLXR_SMALLM_BY_NPAD(__nv_bfloat16, 1, false); }
+#define MLXR_SMALLM_BY_DTYPE(QTV)                                                                          \
+  do {                                                                                                     \
+    if (dtype == MLXR_F16) { if (swiglu) MLXR_SMALLM_BY_NPAD(QTV, __half, 0, true); else MLXR_SMALLM_BY_NPAD(QTV, __half, 0, false); } \
+    else { if (swiglu) MLXR_SMALLM_BY_NPAD(QTV, __nv_bfloat16, 1, true); else MLXR_SMALLM_BY_NPAD(QTV, __nv_bfloat16, 1, false); }     \
+  } while (0)
+  if (qt == MLXR_Q4_K) MLXR_SMALLM_BY_DTYPE(MLXR_Q4_K);
+  else if (qt == MLXR_Q4_0) MLXR_SMALLM_BY_DTYPE(MLXR_Q4_0);
+  else set_error("small-batch kernel: no producer for %s", mlxr_quant_type_name(qt));
+#undef MLXR_SMALLM_BY_DTYPE
 #undef MLXR_SMALLM_BY_NPAD
   return rc;
 }

@@ -1,4 +1,4 @@
-"""Small-batch tensor-core linear (Q4_K, 3 <= M <= 64; csrc/smallm.cu) through the C ABI vs the oracle.
+"""Small-batch tensor-core linear (Q4_K and Q4_0, 3 <= M <= 64; csrc/smallm.cu) through the C ABI vs the oracle.
 
 Gate 2e-2 relative L2.  The tests use 2e-3 for fp16 activations (the weights are converted with
 the shader's own fp16 arithmetic, q_gemm_dequant.metal:244-256) and 1e-2 for bf16 (scale, min and
@@ -23,26 +23,27 @@ def _status():
     return int(st[0])
 
 
-def _run(oracle, M, N, K, dt, bias=False, seed=0, rows=None, twice=False):
+def _run(oracle, M, N, K, dt, bias=False, seed=0, rows=None, twice=False, qt=3):
     import mlxr_b200 as mx
     from mlxr_b200.quantize import quantize
-    packed = quantize(make_weights(N, K, 100 + seed), 3)
+    packed = quantize(make_weights(N, K, 100 + seed), qt)
     xt, xf = make_acts(M, K, 200 + seed, DT[dt])
     bt = bf = None
     if bias:
         bt, bf = make_acts(1, N, 300 + seed, DT[dt])
         bt, bf = bt[0].contiguous(), bf[0]
     xd, wd, bd = xt.cuda(), torch.from_numpy(packed).cuda(), (bt.cuda() if bias else None)
-    y = mx.q_gemm_dequant(xd, wd, M, N, K, mx.QuantType(3), 256, bd)
+    gs = mx._capi.lib.mlxr_default_group_size(qt)
+    y = mx.q_gemm_dequant(xd, wd, M, N, K, mx.QuantType(qt), gs, bd)
     if twice:   # the tile counters must have cleared themselves, and the result must not depend on arrival order
-        y2 = mx.q_gemm_dequant(xd, wd, M, N, K, mx.QuantType(3), 256, bd)
+        y2 = mx.q_gemm_dequant(xd, wd, M, N, K, mx.QuantType(qt), gs, bd)
         assert torch.equal(y, y2)
     torch.cuda.synchronize()
     assert _status() == 0
     yn = y.float().cpu().numpy()
     if rows is not None:
-        return oracle.rel_l2(yn[rows], oracle.linear(xf[rows], packed, N, 3, bf))
-    return oracle.rel_l2(yn, oracle.linear(xf, packed, N, 3, bf))
+        return oracle.rel_l2(yn[rows], oracle.linear(xf[rows], packed, N, qt, bf))
+    return oracle.rel_l2(yn, oracle.linear(xf, packed, N, qt, bf))
 
 
 @pytest.mark.parametrize("dt", ["bf16", "f16"])
@@ -50,6 +51,17 @@ def _run(oracle, M, N, K, dt, bias=False, seed=0, rows=None, twice=False):
                                    (17, 384, 1280), (32, 640, 2048), (33, 200, 512), (64, 1024, 1024)])
 def test_shapes(oracle, dt, M, N, K):
     assert _run(oracle, M, N, K, dt, seed=M, twice=True) <= TIGHT[dt]
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f16"])
+@pytest.mark.parametrize("M,N,K", [(3, 128, 256), (9, 200, 512), (16, 512, 1024), (33, 384, 1280), (64, 1000, 768)])
+def test_q4_0_shapes(oracle, dt, M, N, K):
+    """Q4_0: the same 144 bytes per 256 weights of a row, read as eight 18-byte blocks."""
+    assert _run(oracle, M, N, K, dt, seed=M + 50, twice=True, qt=0, bias=(N == 200)) <= TIGHT[dt]
+
+
+def test_q4_0_decode_shape_sampled_rows(oracle):
+    assert _run(oracle, 32, 5632, 2048, "f16", rows=np.array([0, 17, 31]), seed=8, twice=True, qt=0) <= TIGHT["f16"]
 
 
 @pytest.mark.parametrize("dt", ["bf16", "f16"])
