@@ -16,6 +16,10 @@ __global__ void __launch_bounds__(THREADS) rmsnorm_kernel(const T* __restrict__ 
                                                           T* __restrict__ y, int hidden,
                                                           float eps) {
   __shared__ float red[THREADS / 32];
+  // A kernel launched behind this one with programmatic stream serialization (the linears of the
+  // MLP block) may start its set-up and its weight stream now; it waits for this kernel's
+  // completion before it reads y.  Without such a dependent the instruction does nothing.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const size_t row = blockIdx.x;
   const T* xr = x + row * hidden;
   float v[PER_THREAD];
