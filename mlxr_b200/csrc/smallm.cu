@@ -49,7 +49,10 @@ using namespace tc;
 constexpr int kRows = 128;                 // weight rows per tile (MMA M, TMEM lanes)
 constexpr int kBK = 64;                    // K per operand tile: one 128-byte swizzle row
 constexpr int kStages = 6;                 // converted operand tiles (one 64-wide k-block each) in flight
-constexpr int kMaxXStages = 4, kMaxRawStages = 4;
+constexpr int kMaxXStages = 4, kMaxRawStages = 5;
+#ifndef MLXR_SM_RAW16
+#define MLXR_SM_RAW16 4      // packed super-blocks in flight at the narrowest batch width
+#endif
 constexpr int kRawBytes = kRows * 144;     // 18432
 constexpr int kATile = kRows * kBK * 2;    // 16 KB
 constexpr int kProducerWarps = 16;
@@ -143,7 +146,7 @@ __device__ __forceinline__ uint4 dequant8_bf16x2(uint32_t v, __nv_bfloat162 ss, 
 template <int NPAD> struct Rings {
   // shared memory: 96 KB of converted tiles + X + packed weights must stay under 227 KB
   static constexpr int kXStages = NPAD == 64 ? 2 : NPAD == 32 ? 3 : 4;      // X tiles of whole units in flight
-  static constexpr int kRawStages = NPAD == 64 ? 3 : 4;                     // packed super-blocks in flight
+  static constexpr int kRawStages = NPAD == 64 ? 3 : NPAD == 16 ? MLXR_SM_RAW16 : 4;   // packed super-blocks in flight
   static constexpr int kXTile = NPAD * kBK * 2;                             // one k-block of X
   static constexpr int kXUnit = 4 * kXTile;                                 // the four k-blocks of a unit
   static constexpr size_t kBytes = (size_t)kStages * kATile + (size_t)kXStages * kXUnit + (size_t)kRawStages * kRawBytes;
