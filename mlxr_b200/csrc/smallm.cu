@@ -17,14 +17,20 @@
 //   the end of one tile, whole tiles and the start of another; the sums of a tile that several
 //   CTAs share are parked as fp32 partials and added, in CTA order, by whichever of them
 //   arrives last (a counter per tile, nobody waits).
-// * One TMA box per unit brings the tile's 128 x 144 bytes of one super-block (a three-deep
-//   ring: 54 KB in flight per SM); 16 producer warps convert them into the 128-byte-swizzled
-//   K-major operand tiles of four 64-wide k-blocks (a six-deep ring), thread (row, k-block);
-//   a second copy warp brings the X tiles a unit at a time (their own ring, two to four units
-//   ahead: fetched per k-block behind the MMAs, their L2 latency was the whole kernel's pace);
-//   one thread issues the MMAs; four epilogue
-//   warps drain the accumulator, which is double-buffered in tensor memory so that the next
-//   tile's MMAs do not wait for them.
+// * One TMA box per unit brings the tile's 128 x 144 bytes of one super-block (a ring three or
+//   four deep: 54-72 KB in flight per SM); 16 producer warps, thread (row, k-block), convert
+//   them into the 128-byte-swizzled K-major operand tiles of the unit's four 64-wide k-blocks
+//   (a six-deep ring); a second copy warp brings the X tiles a unit at a time (their own ring,
+//   two to four units ahead: fetched per k-block behind the MMAs, their L2 round trip was the
+//   kernel's pace); four issuer warps, one per k-block, issue the MMAs into accumulators of
+//   their own (one issuer for all four needed 0.4 us per k-block and set the pace); four
+//   epilogue warps add the four accumulators and drain them, double-buffered in tensor memory
+//   so that the next tile's MMAs do not wait for them.
+// * Gate/up form: a tile holds 16 gate rows and 16 up rows per TMEM lane quarter (eight TMA
+//   boxes from two tensor maps) and the epilogue stores SiLU(gate) * up.
+// * Launched with programmatic stream serialization: set-up, the weight stream and the
+//   conversion start while the previous kernel of the stream drains; the X loads and everything
+//   the epilogue reads or writes wait for griddepcontrol.wait.
 // * Every wait is bounded (tc::mbar_wait); a role that gives up sets a flag that the others
 //   poll, copies in flight are awaited, tensor memory is freed, and the status word reports
 //   MLXR_ERR_TIMEOUT.
