@@ -127,6 +127,10 @@ __device__ __forceinline__ float swish_fast(float x) {
   return x * (x >= 0.0f ? s : e * s);
 }
 
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
 __device__ __forceinline__ void epi_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 // Eight consecutive weights (one word of nibbles) as four bf16 pairs, bf16 arithmetic throughout:
@@ -251,6 +255,7 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
     int use = 0;               // which use of that stage this is: (4 i + j) / 6
     int r = 0;
     uint32_t rpar = 0;
+    const uint32_t a_row0 = smem_u32(aring) + (uint32_t)p * 128u + (uint32_t)((p & 7) << 4);
     for (int i = 0; i < nunits; i++) {
 #ifdef MLXR_TUNING
       if (!(P.debug & 2))
@@ -273,10 +278,12 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
         // second (scale, min) pair, offsets 0, 2 and 3 the first (q_gemm_dequant.metal:222-242)
         const __half d = __ushort_as_half((unsigned short)(ch.x & 0xFFFFu));
         const __half dmin = __ushort_as_half((unsigned short)(ch.x >> 16));
-        const uint32_t t24 = (j & 2) ? ((ch.y >> 24) | ((ch.z & 0xFFFFu) << 8)) : (ch.y & 0xFFFFFFu);
-        const uint32_t b0 = t24 & 0xFFu, b1 = (t24 >> 8) & 0xFFu, b2 = (t24 >> 16) & 0xFFu;
-        const int sc_a = (int)(b0 & 0x3Fu), mn_a = (int)(((b0 >> 6) | ((b1 & 0x0Fu) << 2)) & 0x3Fu);
-        const int sc_b = (int)(((b1 >> 4) | ((b2 & 0x03u) << 4)) & 0x3Fu), mn_b = (int)((b2 >> 2) & 0x3Fu);
+        // The three bytes hold four consecutive 6-bit fields: scale and min of the first pair, then of
+        // the second (the shader's byte-wise extraction, (b0 & 63), (b0 >> 6 | (b1 & 15) << 2),
+        // (b1 >> 4 | (b2 & 3) << 4), (b2 >> 2), reads exactly bits 0-5, 6-11, 12-17, 18-23)
+        const uint32_t t24 = __funnelshift_r(ch.y, ch.z, (j & 2) ? 24 : 0);
+        const int sc_a = (int)(t24 & 0x3Fu), mn_a = (int)((t24 >> 6) & 0x3Fu);
+        const int sc_b = (int)((t24 >> 12) & 0x3Fu), mn_b = (int)((t24 >> 18) & 0x3Fu);
         const bool second = (j & 1) == 0;      // sub-block 2 j + 1 has offset 1 only for even j
         ss0 = __hmul_rn(__int2half_rn(sc_a), d); sm0 = __hmul_rn(__int2half_rn(mn_a), dmin);
         ss1 = __hmul_rn(__int2half_rn(second ? sc_b : sc_a), d); sm1 = __hmul_rn(__int2half_rn(second ? mn_b : mn_a), dmin);
@@ -300,29 +307,30 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
 
       // the MMAs of the stage's previous use (the other group's) must be done
       if (use > 0 && !__all_sync(0xffffffffu, mbar_wait(smem_u32(&sh->empty[s][(use - 1) & 1]), ((use - 1) >> 1) & 1, dead))) break;   // warp-uniform
-      uint8_t* arow = aring + (size_t)s * kATile + (size_t)p * 128;
-      // 16-byte chunk c of row p sits at chunk position c ^ (p & 7) (128-byte swizzle)
+      // 16-byte chunk c of row p sits at chunk position c ^ (p & 7) (128-byte swizzle): with the row
+      // base 128-byte aligned, its shared-memory address is (row base + 16 (p & 7)) ^ 16 c
+      const uint32_t arow = a_row0 + (uint32_t)s * kATile;
 #ifdef MLXR_TUNING
       if (P.debug & 1) {
 #pragma unroll
-        for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(arow + ((c ^ (p & 7)) << 4)) = make_uint4(wa[0], wa[1], wa[2], wa[3]);
+        for (int c = 0; c < 4; c++) sts128(arow ^ (uint32_t)(c << 4), make_uint4(wa[0], wa[1], wa[2], wa[3]));
 #pragma unroll
-        for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(arow + (((4 + c) ^ (p & 7)) << 4)) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+        for (int c = 0; c < 4; c++) sts128(arow ^ (uint32_t)((4 + c) << 4), make_uint4(wb[0], wb[1], wb[2], wb[3]));
       } else
 #endif
       if constexpr (BF == 0) {
         const __half2 s0 = __half2half2(ss0), m0 = __half2half2(sm0), s1 = __half2half2(ss1), m1 = __half2half2(sm1);
 #pragma unroll
-        for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(arow + ((c ^ (p & 7)) << 4)) = dequant8_f16(wa[c], s0, m0);
+        for (int c = 0; c < 4; c++) sts128(arow ^ (uint32_t)(c << 4), dequant8_f16(wa[c], s0, m0));
 #pragma unroll
-        for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(arow + (((4 + c) ^ (p & 7)) << 4)) = dequant8_f16(wb[c], s1, m1);
+        for (int c = 0; c < 4; c++) sts128(arow ^ (uint32_t)((4 + c) << 4), dequant8_f16(wb[c], s1, m1));
       } else {
         const __nv_bfloat162 s0 = __float2bfloat162_rn(__half2float(ss0)), m0 = __float2bfloat162_rn(__half2float(sm0));
         const __nv_bfloat162 s1 = __float2bfloat162_rn(__half2float(ss1)), m1 = __float2bfloat162_rn(__half2float(sm1));
 #pragma unroll
-        for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(arow + ((c ^ (p & 7)) << 4)) = dequant8_bf16x2(wa[c], s0, m0);
+        for (int c = 0; c < 4; c++) sts128(arow ^ (uint32_t)(c << 4), dequant8_bf16x2(wa[c], s0, m0));
 #pragma unroll
-        for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(arow + (((4 + c) ^ (p & 7)) << 4)) = dequant8_bf16x2(wb[c], s1, m1);
+        for (int c = 0; c < 4; c++) sts128(arow ^ (uint32_t)((4 + c) << 4), dequant8_bf16x2(wb[c], s1, m1));
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
