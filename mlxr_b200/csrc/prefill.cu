@@ -385,16 +385,11 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_constant_
         // only o == 1 takes the second pair (offsets 2 and 3 alias offset 0, q_gemm_dequant.metal:222-242)
         const __half d = __ushort_as_half((unsigned short)(ch.x & 0xFFFFu));
         const __half dmin = __ushort_as_half((unsigned short)(ch.x >> 16));
-        const uint32_t t24 = (kb & 2) ? ((ch.y >> 24) | ((ch.z & 0xFFFFu) << 8)) : (ch.y & 0xFFFFFFu);
-        const uint32_t b0 = t24 & 0xFFu, b1 = (t24 >> 8) & 0xFFu, b2 = (t24 >> 16) & 0xFFu;
-        int sc, mn;
-        if (((kb & 1) == 0) && hb == 1) {
-          sc = (int)(((b1 >> 4) | ((b2 & 0x03u) << 4)) & 0x3Fu);
-          mn = (int)((b2 >> 2) & 0x3Fu);
-        } else {
-          sc = (int)(b0 & 0x3Fu);
-          mn = (int)(((b0 >> 6) | ((b1 & 0x0Fu) << 2)) & 0x3Fu);
-        }
+        // the group's three bytes are four consecutive 6-bit fields (scale, min of the first pair, then
+        // of the second): the shader's byte-wise extraction reads exactly bits 0-5, 6-11, 12-17, 18-23
+        const uint32_t t24 = __funnelshift_r(ch.y, ch.z, (kb & 2) ? 24 : 0);
+        const uint32_t pair = (((kb & 1) == 0) && hb == 1) ? (t24 >> 12) : t24;
+        const int sc = (int)(pair & 0x3Fu), mn = (int)((pair >> 6) & 0x3Fu);
         const __half ssh = __hmul_rn(__int2half_rn(sc), d), smh = __hmul_rn(__int2half_rn(mn), dmin);
         const uint32_t w4[4] = {cq.x, cq.y, cq.z, cq.w};
         if constexpr (BF == 0) {
