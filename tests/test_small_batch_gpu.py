@@ -94,3 +94,22 @@ def test_non_finite_input_propagates():
     y = mx.q_gemm_dequant(x.cuda(), packed, M, N, K, mx.QuantType(3), 256, None).float().cpu()
     assert torch.isnan(y[2]).all()
     assert torch.isfinite(y[[0, 1, 3, 4, 5]]).all()
+
+
+def test_bit_identical_over_many_launches():
+    """Launches of different geometry back to back, many times: every result of a shape equals the
+    first one bit for bit (tiles shared between CTAs are summed in CTA order, whatever the arrival
+    order; a stale barrier phase or a counter left over from another shape would show here)."""
+    import mlxr_b200 as mx
+    from mlxr_b200.quantize import quantize
+    shapes = [(64, 1536, 2048), (32, 640, 3584), (9, 1024, 1024)]
+    data = []
+    for i, (M, N, K) in enumerate(shapes):
+        w = torch.from_numpy(quantize(make_weights(N, K, 40 + i), 3)).cuda()
+        x = torch.randn(M, K, generator=torch.Generator().manual_seed(i)).to(torch.bfloat16).cuda()
+        data.append((x, w, M, N, K, mx.q_gemm_dequant(x, w, M, N, K, mx.QuantType(3), 256, None).clone()))
+    for _ in range(60):
+        for x, w, M, N, K, first in data:
+            assert torch.equal(mx.q_gemm_dequant(x, w, M, N, K, mx.QuantType(3), 256, None), first)
+    torch.cuda.synchronize()
+    assert _status() == 0
