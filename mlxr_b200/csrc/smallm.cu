@@ -79,7 +79,7 @@ struct Params {
   float* partials;     // [ntiles][maxc][NPAD][128] fp32
   uint32_t* counters;  // one per tile, self-clearing
   unsigned long long* trace;   // tuning: 32 time stamps per CTA
-  int debug;           // tuning probes (builds with MLXR_TUNING): 1 no conversion math, 2 no weight copies, 4 no MMAs
+  int debug;           // tuning probes (builds with MLXR_TUNING): 1 no conversion math, 2 no weight copies, 4 no MMAs, 8 plain arrives, 16 no X copies after the first ring fill
 };
 
 struct Shared {
@@ -424,6 +424,14 @@ qgemm_smallm_kernel(const __grid_constant__ CUtensorMap xmap, const __grid_const
       for (int i = 0; i < nunits; i++) {
         if (!mbar_wait(smem_u32(&sh->x_empty[xs]), par ^ 1u, dead)) break;
         const uint32_t bar = smem_u32(&sh->x_full[xs]);
+#ifdef MLXR_TUNING
+        if ((P.debug & 16) && i >= kXStages) {      // probe: reuse the tiles already in the ring
+          mbar_arrive(bar);
+          if (++sb == P.nsb) sb = 0;
+          if (++xs == kXStages) { xs = 0; par ^= 1u; }
+          continue;
+        }
+#endif
         mbar_expect_tx(bar, kXUnit);
 #pragma unroll
         for (int jj = 0; jj < 4; jj++)
