@@ -624,7 +624,15 @@ int smallm_plan(int M, int rows, int K, int* grid, int* maxc, size_t* partial_by
   if (int r = device_sms(&sms)) return r;
   const int nsb = K / 256, ntiles = (N + smallm::kRows - 1) / smallm::kRows;
   const long long U = (long long)ntiles * nsb;
-  const int G = (int)std::min<long long>(sms, U);
+  int G = (int)std::min<long long>(sms, U);
+  // Equal ranges make most tiles shared, and a shared tile costs its CTAs an epilogue whose length
+  // grows with the padded batch width (partial sums stored, counted, re-read by the last arriver:
+  // measured about 3 us at width 16 and 7 to 15 us at width 64).  When there is at most one tile
+  // per SM, one whole tile per CTA needs no fix-up at all and only lengthens the loop from U / G
+  // units to K / 256: taken when that difference (about 1 us per unit) is below 0.13 us per
+  // column of the padded width (measured at N = 14336, K = 4096: batch 32 23.1 -> 19.4 us,
+  // batch 64 29.4 -> 21.5 us; at width 16 the equal ranges stay ahead, 19.1 us).
+  if (ntiles <= sms && (double)nsb - (double)U / G < 0.13 * smallm_npad(M)) G = ntiles;
   int mc = 1;
   for (int t = 0; t < ntiles; t++)
     mc = std::max(mc, smallm::unit_owner(U, G, (long long)(t + 1) * nsb - 1) - smallm::unit_owner(U, G, (long long)t * nsb) + 1);
